@@ -405,6 +405,54 @@ int pk_tp_ipc_export(void* dev_ptr, void* handle_out_64);
 int pk_tp_ipc_open(const void* handle_64, void** dev_ptr_out);
 int pk_tp_ipc_close(void* dev_ptr);
 
+/* =============== fp32-residual, latent-attention and mixture-of-experts ops ===============
+ * Building blocks for decoder designs that keep the residual stream in fp32, norm the OUTPUT of each sublayer, attend
+ * over a compressed (latent) paged cache and route tokens to experts.  `f32` selects the element type of activations,
+ * weights and cache behind the void pointers: 0 = bf16, 1 = float (everything in true fp32).  Arithmetic is fp32 in
+ * both; a value is rounded once, when stored.  Activations are [tokens, features] row-major.  int: cudaError, -1 =
+ * invalid argument, -2 = shape outside the kernel's range. */
+/* x[t] = float(embed[ids[t]]) (fp32 residual) and xa[t] = the same row in the element type (next projection's input) */
+int pk_res32_embed(const void* embed, const int* token_ids, float* x, void* xa, int width, int tokens, int f32, pk_stream st);
+/* x[t] += y[t] / sqrt(mean(y[t]^2) + eps) * (1 + w);  xa[t] = element-type copy of the new x[t].  y: element type, or float when y_is_f32 */
+int pk_res32_offset_norm_add(const void* y, int y_is_f32, const void* w, float* x, void* xa, int width, int tokens, float eps, int f32,
+                             pk_stream st);
+/* out[r] = x[rows[r]] / rms * (1 + w) in the element type (last norm, only for the rows whose logits are wanted) */
+int pk_res32_offset_norm_rows(const float* x, const int* rows, const void* w, void* out, int width, int n_rows, float eps, int f32, pk_stream st);
+/* out[t][m] = W[m] . x[t] with fp32 input, accumulation and output (router logits, gates): M small */
+int pk_res32_skinny_proj(const void* W, const float* x, float* out, int M, int K, int tokens, int f32, pk_stream st);
+/* kind 0: out[t][f] = silu(in[t][f]) * in[t][F + f] (in [tokens, 2F]);  kind 1: out[t][f] = relu(in[t][f])^2 (in [tokens, F]) */
+int pk_act(const void* in, void* out, int F, int tokens, int kind, int f32, pk_stream st);
+int pk_convert(const void* in, int in_f32, void* out, int out_f32, long n, pk_stream st);
+/* Strided batched product in plain FMA arithmetic: C[b][i][j] = f(row_scale[i*ld_scale + b]) * sum_k A[b*bsA + i*lda + k] * B[b*bsB + k*sbk + j*sbn],
+ * C at b*bsC + i*ldc + j.  scale_kind 1: f = identity, 2: f = logistic; row_scale may be NULL.  With f32 = 1 this is the
+ * exact-fp32 linear layer (B = W [cols, K]: sbk 1, sbn K). */
+int pk_gemm_strided(const void* A, const void* B, void* C, const float* row_scale, int rows, int cols, int K, long lda, long sbk, long sbn,
+                    long ldc, int batch, long bsA, long bsB, long bsC, int ld_scale, int scale_kind, int f32, pk_stream st);
+/* Rotate-half rotary embedding of a slice of every head: out[t,h,out_off+i] = rot(in[t,h,in_off+i]), i < width; the first
+ * `dims` entries rotate in pairs (i, i+dims/2) by positions[t] * freq[i] with cos and sin multiplied by `mag`, the rest pass.
+ * freq [dims/2] is a device table built by the host (plain or YaRN-blended frequencies). */
+int pk_rope_slice(const void* in, void* out, const int* positions, const float* freq, float mag, int tokens, int heads, int in_stride,
+                  int in_off, int out_stride, int out_off, int width, int dims, int f32, pk_stream st);
+/* Paged latent cache: token t of request req[t] at position p lives in page pages[page_off[req[t]] + p / page_size], slot
+ * p % page_size, at cache + page * page_stride + slot * (rank + rot).  Append: c = dkv[t][:rank] / rms * norm_w, then the
+ * rotated dkv[t][rank:]. */
+int pk_latent_kv_append(const void* dkv, const void* norm_w, const int* positions, const int* req, const int* page_off, const int* pages,
+                        void* cache, long page_stride, int page_size, int rank, int rot, int dims, const float* freq, float mag, float eps,
+                        int tokens, int f32, pk_stream st);
+/* out[t,h,:rank] = sum_j softmax_j((qa[t,h] . [c_j | kr_j]) * scale; with exp(sink[h]) added to the denominator) c_j over the
+ * request's cached positions j <= positions[t].  qa [tokens, heads, rank + rot] holds the query already folded onto the latent. */
+int pk_latent_attention(const void* qa, const void* cache, const void* sink, const int* positions, const int* req, const int* page_off,
+                        const int* pages, void* out, long page_stride, int page_size, int tokens, int heads, int rank, int rot, float scale,
+                        int f32, pk_stream st);
+/* Group-limited top-k router over fp32 logits [tokens, experts]: ids / weights [tokens, top] (see moe.cu) */
+int pk_router_grouped_topk(const float* logits, int* ids, float* weights, int tokens, int experts, int top, int groups, int keep, float scale,
+                           pk_stream st);
+/* hid[t,k,:] = relu(W_up[ids[t,k]] xa[t])^2, W_up [experts, ff, width] */
+int pk_moe_up_relu2(const void* xa, const void* w_up, const int* ids, void* hid, int tokens, int top, int width, int ff, int f32, pk_stream st);
+/* y[t] = sum_k weights[t,k] W_down[ids[t,k]] hid[t,k,:] (+ logistic(shared_gate[t]) * shared[t] when shared != NULL); y fp32 */
+int pk_moe_down_combine(const void* hid, const void* w_down, const int* ids, const float* weights, const void* shared,
+                        const float* shared_gate, float* y, int tokens, int top, int width, int ff, int f32, pk_stream st);
+
 #ifdef __cplusplus
 }
 #endif

@@ -40,19 +40,42 @@ def _run(cmd: list[str]) -> None:
         raise RuntimeError(f"build failed: {cmd[0]} ... {cmd[-1]}")
 
 
-def kernel_sources() -> list[str]:
-    return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cu"))
+# What one design needs when nothing is built yet (a fresh checkout asked to serve that design compiles these files and no
+# others): kernel sources, host sources.  A later full build adds the rest and links both libraries again.
+PARTS_OF = {
+    "Vamadra": (("runtime.cu", "gemm.cu", "gemm2.cu", "gemv.cu", "sampling.cu", "residual32_ops.cu", "latent_attention.cu", "moe.cu"),
+                ("qwen3_host.cpp", "vamadra_host.cpp")),
+}
+MANIFEST = os.path.join(OBJ, "linked.txt")
 
 
-def host_sources() -> list[str]:
+def kernel_sources(only=None) -> list[str]:
+    return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cu") and (only is None or f in only))
+
+
+def host_sources(only=None) -> list[str]:
     d = os.path.join(CSRC, "host")
     if not os.path.isdir(d):
         return []
-    return sorted(os.path.join(d, f) for f in os.listdir(d) if f.endswith(".cpp"))
+    return sorted(os.path.join(d, f) for f in os.listdir(d) if f.endswith(".cpp") and (only is None or f in only))
 
 
-def build(force: bool = False, verbose: bool = False) -> None:
+def _linked() -> set:
+    try:
+        with open(MANIFEST) as f:
+            return set(f.read().split())
+    except OSError:
+        return set()
+
+
+def build(force: bool = False, verbose: bool = False, parts=None) -> None:
+    """Build what is stale.  ``parts`` = (kernel files, host files) restricts a FIRST build to those sources; once libraries
+    that hold at least these parts exist, nothing is rebuilt for them (sources newer than their objects still are)."""
     os.makedirs(OBJ, exist_ok=True)
+    have = _linked()
+    if parts is not None and os.path.exists(KERNEL_LIB) and os.path.exists(HOST_LIB) and set(parts[0]) | set(parts[1]) <= have:
+        parts = tuple(sorted(f for f in have if f.endswith(ext)) for ext in (".cu", ".cpp"))  # keep what is linked, refresh if stale
+    konly, honly = (None, None) if parts is None else (set(parts[0]), set(parts[1]))
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     headers.append(os.path.join(HERE, "..", "include", "pegainfer_kernels.h"))
     hdir = os.path.join(CSRC, "host")
@@ -60,7 +83,7 @@ def build(force: bool = False, verbose: bool = False) -> None:
         headers += [os.path.join(hdir, f) for f in os.listdir(hdir) if f.endswith((".hpp", ".h"))]
 
     jobs, objs = [], []
-    for src in kernel_sources():
+    for src in kernel_sources(konly):
         obj = os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")
         objs.append(obj)
         if force or _stale(obj, [src] + headers):
@@ -70,17 +93,22 @@ def build(force: bool = False, verbose: bool = False) -> None:
     if jobs:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(_run, jobs))
-    if force or jobs or _stale(KERNEL_LIB, objs):
+    names = {os.path.basename(p) for p in kernel_sources(konly)} | {os.path.basename(p) for p in host_sources(honly)}
+    relink = names != have
+    if force or jobs or relink or _stale(KERNEL_LIB, objs):
         _run([NVCC, *ARCH, "-shared", "-o", KERNEL_LIB, *objs, "-lcudart", "-ccbin", "/usr/bin/g++"])
 
-    hsrcs = host_sources()
-    if hsrcs and (force or _stale(HOST_LIB, hsrcs + headers)):
+    hsrcs = host_sources(honly)
+    if hsrcs and (force or relink or _stale(HOST_LIB, hsrcs + headers)):
         if verbose:
             print("[pegainfer_b200.build] compiling the C++ host mirror", flush=True)
         _run(["/usr/bin/g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-pthread",
               "-I/usr/local/cuda/include", "-I" + os.path.join(HERE, "..", "include"), *hsrcs,
               "-o", HOST_LIB, "-L/usr/local/cuda/lib64", "-lcudart", "-ldl",
               "-Wl,-rpath,/usr/local/cuda/lib64"])
+    if relink or not os.path.exists(MANIFEST):
+        with open(MANIFEST, "w") as f:
+            f.write("\n".join(sorted(names)) + "\n")
 
 
 if __name__ == "__main__":

@@ -1,0 +1,638 @@
+// C++ host of the Vamadra design: a decoder whose layers are listed one by one in the checkpoint's configuration, each
+// with a latent-attention mixer (compressed paged cache, shared rotated key part, per-head softmax sink, logistic
+// output gate, optional reuse of an earlier layer's cache) and a dense or mixture-of-experts feed-forward, on an fp32
+// residual stream with the norm on the sublayer's output.
+//
+// Same structure as the other hosts in this folder: kernels are reached only through the C ABI
+// (include/pegainfer_kernels.h) resolved with dlopen; paging reuses pq::PagePool / pq::KvState; a step is planned and
+// validated first and committed last; one packed metadata block per step is uploaded with a single copy.
+//
+// One entry point runs everything: step() takes a ragged batch -- for each live request its next tokens, whether that
+// is a portion of a prompt or one decoded token -- appends to the cache and returns logits for the rows asked for.
+// Element type of weights / activations / cache is bf16 (tensor-core GEMMs of this library) or float (plain FMA
+// kernels, no reduced-precision matrix mode); softmax, norms, routers and the residual sum are fp32 in both.
+#include <dlfcn.h>
+
+#include <algorithm>
+#include <chrono>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <set>
+#include <string>
+
+#include "qwen3_host.hpp"
+
+namespace pv {
+
+using pq::DeviceBuf;
+
+struct LayerCfg {  // mirrored by ctypes in pegainfer_b200/vamadra.py
+  int heads, dim, rot_dim, vdim, kv_rank, kv_from;  // kv_from < 0: the layer owns its cache
+  int rot_dims;                                      // rotated entries of the rot_dim slice
+  float rot_base, scale;
+  int has_scaling;
+  float s_factor, s_original, s_fast, s_slow;  // YaRN
+  int mlp_kind;                                // 0 none, 1 dense (SwiGLU), 2 mixture of experts
+  int ff;                                      // dense: hidden size
+  int experts, top, groups, keep;
+  float route_scale;
+  int expert_ff, shared_ff;  // shared_ff 0: no shared expert
+};
+struct ModelCfg {
+  int vocab, width, n_layers;
+  float eps;
+  int f32, page_size, num_pages, max_requests, device, enable_pdl;
+};
+
+struct Lib {
+  void* handle = nullptr;
+#define PV_FN(name) decltype(&::name) name = nullptr;
+  PV_FN(cuda_set_device) PV_FN(cublas_init) PV_FN(cublas_destroy) PV_FN(gemm_cuda) PV_FN(flashinfer_top1_cuda) PV_FN(pk_b200_set_pdl)
+  PV_FN(pk_b200_launch_count) PV_FN(pk_res32_embed) PV_FN(pk_res32_offset_norm_add) PV_FN(pk_res32_offset_norm_rows)
+  PV_FN(pk_res32_skinny_proj) PV_FN(pk_act) PV_FN(pk_convert) PV_FN(pk_gemm_strided) PV_FN(pk_rope_slice) PV_FN(pk_latent_kv_append)
+  PV_FN(pk_latent_attention) PV_FN(pk_router_grouped_topk) PV_FN(pk_moe_up_relu2) PV_FN(pk_moe_down_combine)
+#undef PV_FN
+  std::string load(const std::string& p) {
+    handle = dlopen(p.c_str(), RTLD_NOW | RTLD_LOCAL);
+    if (!handle) return std::string("dlopen failed: ") + dlerror();
+    std::string missing;
+#define PV_REQ(name)                                             \
+  name = reinterpret_cast<decltype(name)>(dlsym(handle, #name)); \
+  if (!name) missing += std::string(" ") + #name;
+    PV_REQ(cuda_set_device) PV_REQ(cublas_init) PV_REQ(cublas_destroy) PV_REQ(gemm_cuda) PV_REQ(flashinfer_top1_cuda) PV_REQ(pk_b200_set_pdl)
+    PV_REQ(pk_b200_launch_count) PV_REQ(pk_res32_embed) PV_REQ(pk_res32_offset_norm_add) PV_REQ(pk_res32_offset_norm_rows)
+    PV_REQ(pk_res32_skinny_proj) PV_REQ(pk_act) PV_REQ(pk_convert) PV_REQ(pk_gemm_strided) PV_REQ(pk_rope_slice) PV_REQ(pk_latent_kv_append)
+    PV_REQ(pk_latent_attention) PV_REQ(pk_router_grouped_topk) PV_REQ(pk_moe_up_relu2) PV_REQ(pk_moe_down_combine)
+#undef PV_REQ
+    return missing.empty() ? "" : "kernel library " + p + " lacks:" + missing;
+  }
+  ~Lib() {
+    if (handle) dlclose(handle);
+  }
+};
+
+struct Mat {
+  DeviceBuf d;
+  int rows = 0, cols = 0;
+};
+struct Layer {
+  LayerCfg c{};
+  Mat norm1, norm2, q, dkv, dkv_norm, uk, uv, sink, g, o;  // mixer
+  Mat gate_up, down;                                       // dense: [gate ; up] stacked
+  Mat e_up, e_down, router, s_up, s_down, s_gate;          // experts stacked [experts * ff, width] / [experts * width, ff]
+  DeviceBuf freq;                                          // [rot_dims / 2] fp32 angular frequencies
+  float mag = 1.f;
+  int owner = -1;       // layer whose cache this layer reads (itself when it owns one)
+  int64_t cache_off = 0;  // element offset of the owner's block inside a page
+  std::set<std::string> got;
+};
+
+struct Model {
+  Lib k;
+  ModelCfg c{};
+  std::vector<Layer> layers;
+  std::string err;
+  cudaStream_t st = nullptr;
+  int es = 2;  // element size
+  Mat embed, head, final_norm;
+  DeviceBuf cache;
+  int64_t page_stride = 0;
+  pq::PagePool pool;
+  std::vector<pq::KvState> reqs;
+  bool finalized = false;
+  // per-step scratch, grown to the largest step seen
+  int cap_t = 0, cap_r = 0;
+  DeviceBuf x, xa, q, dkv, qa, gate, olat, ao, mix, gu, act, z, ids, wts, hid, yf, sgl, sh, xr, logits_e, logits_f, logits_bf, sampled_d, top1_val,
+      top1_states, trail;
+  DeviceBuf meta_d;
+  int* meta_h = nullptr;
+  size_t meta_cap = 0;
+  int* sampled_h = nullptr;
+  bool keep_trail = false;
+  int trail_tokens = 0;
+  // widest layer
+  int mx_q = 0, mx_dkv = 0, mx_qa = 0, mx_h = 0, mx_olat = 0, mx_ao = 0, mx_gu = 0, mx_act = 0, mx_e = 0, mx_top = 0, mx_hid = 0;
+
+  bool fail(const std::string& m) {
+    err = m;
+    return false;
+  }
+  bool cu(cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return true;
+    err = std::string(what) + ": " + cudaGetErrorString(e);
+    return false;
+  }
+  bool rc(int r, const char* what) {
+    if (r == 0) return true;
+    err = std::string(what) + " failed (" + (r > 0 ? cudaGetErrorString((cudaError_t)r) : r == -1 ? "invalid argument" : "shape out of range") + ")";
+    return false;
+  }
+  ~Model() {
+    if (st) cudaStreamSynchronize(st);
+    if (meta_h) cudaFreeHost(meta_h);
+    if (sampled_h) cudaFreeHost(sampled_h);
+    if (k.cublas_destroy) k.cublas_destroy();
+    if (st) cudaStreamDestroy(st);
+  }
+  bool configure(const ModelCfg& mc, const LayerCfg* lc);
+  bool put(Mat& m, int rows, int cols, int row0, const void* src, int src_rows, const std::string& name, int got_rows, int got_cols);
+  bool load_tensor(const std::string& name, const void* data, int rows, int cols, int is_f32);
+  bool finalize();
+  bool ensure_scratch(int T, int R);
+  bool lin(const Mat& W, const void* X, void* Y, int N);
+  bool run_layer(int li, int T, const int* d_pos, const int* d_req, const int* d_poff, const int* d_pages);
+  bool step(int n, const int* tokens, const int* lens, const int* rids, int n_rows, const int* rows, int want_sample);
+};
+
+static std::string lname(int i, const char* s) { return "l" + std::to_string(i) + "." + s; }
+
+bool Model::configure(const ModelCfg& mc, const LayerCfg* lc) {
+  c = mc;
+  es = c.f32 ? 4 : 2;
+  if (c.vocab <= 0 || c.width <= 0 || c.n_layers <= 0) return fail("vocab, width and the number of layers must be positive");
+  if (c.page_size <= 0) c.page_size = 16;
+  if (c.max_requests <= 0) c.max_requests = 4;
+  layers.resize(c.n_layers);
+  int64_t off = 0;
+  for (int i = 0; i < c.n_layers; ++i) {
+    Layer& L = layers[i];
+    L.c = lc[i];
+    const LayerCfg& a = L.c;
+    if (a.heads <= 0 || a.dim <= 0 || a.vdim <= 0 || a.kv_rank <= 0 || a.rot_dim < 0) return fail(lname(i, "mixer: sizes must be positive"));
+    if (a.rot_dims < 0 || a.rot_dims > a.rot_dim || (a.rot_dims & 1)) return fail(lname(i, "mixer: rot.dims must be even and at most rot_dim"));
+    if (a.kv_rank > 512) return fail(lname(i, "mixer: kv_rank above 512 is outside the attention kernel's range"));
+    if (a.kv_from >= 0) {
+      if (a.kv_from >= i || layers[a.kv_from].c.kv_from >= 0) return fail(lname(i, "mixer: kv_from must name an earlier layer that owns a cache"));
+      const LayerCfg& o = layers[a.kv_from].c;
+      if (o.kv_rank != a.kv_rank || o.rot_dim != a.rot_dim) return fail(lname(i, "mixer: kv_rank / rot_dim differ from the layer it borrows from"));
+      L.owner = a.kv_from;
+      L.cache_off = layers[a.kv_from].cache_off;
+    } else {
+      L.owner = i;
+      L.cache_off = off;
+      off += (int64_t)c.page_size * (a.kv_rank + a.rot_dim);
+    }
+    if (a.mlp_kind == 1 && a.ff <= 0) return fail(lname(i, "mlp: ff must be positive"));
+    if (a.mlp_kind == 2) {
+      if (a.experts <= 0 || a.top <= 0 || a.top > 32 || a.expert_ff <= 0 || a.groups <= 0 || a.experts % a.groups || a.keep <= 0 || a.keep > a.groups ||
+          a.top > a.keep * (a.experts / a.groups))
+        return fail(lname(i, "mlp: inconsistent router (experts, top, groups)"));
+    }
+    mx_q = std::max(mx_q, a.heads * (a.dim + a.rot_dim));
+    mx_dkv = std::max(mx_dkv, a.kv_rank + a.rot_dim);
+    mx_qa = std::max(mx_qa, a.heads * (a.kv_rank + a.rot_dim));
+    mx_h = std::max(mx_h, a.heads);
+    mx_olat = std::max(mx_olat, a.heads * a.kv_rank);
+    mx_ao = std::max(mx_ao, a.heads * a.vdim);
+    if (a.mlp_kind == 1) {
+      mx_gu = std::max(mx_gu, 2 * a.ff);
+      mx_act = std::max(mx_act, a.ff);
+    } else if (a.mlp_kind == 2) {
+      mx_gu = std::max(mx_gu, a.shared_ff);
+      mx_act = std::max(mx_act, a.shared_ff);
+      mx_e = std::max(mx_e, a.experts);
+      mx_top = std::max(mx_top, a.top);
+      mx_hid = std::max(mx_hid, a.top * a.expert_ff);
+    }
+  }
+  page_stride = off;
+  return true;
+}
+
+// upload `src_rows` rows into rows [row0, row0 + src_rows) of a [rows, cols] matrix that is allocated on first use
+bool Model::put(Mat& m, int rows, int cols, int row0, const void* src, int src_rows, const std::string& name, int got_rows, int got_cols) {
+  if (got_rows != src_rows || got_cols != cols) {
+    char b[256];
+    snprintf(b, sizeof b, "%s: shape [%d, %d] does not match the [%d, %d] the configuration implies", name.c_str(), got_rows, got_cols, src_rows, cols);
+    return fail(b);
+  }
+  if (!m.d.ptr) {
+    m.rows = rows;
+    m.cols = cols;
+    if (!m.d.alloc_zeros((size_t)rows * cols * es)) return fail("allocation failed for " + name);
+  }
+  return cu(cudaMemcpy((char*)m.d.ptr + (size_t)row0 * cols * es, src, (size_t)src_rows * cols * es, cudaMemcpyDefault), name.c_str());
+}
+
+bool Model::load_tensor(const std::string& name, const void* data, int rows, int cols, int is_f32) {
+  if ((is_f32 != 0) != (c.f32 != 0)) return fail(name + ": element type differs from the model's");
+  const int W = c.width;
+  if (name == "embed") return put(embed, c.vocab, W, 0, data, c.vocab, name, rows, cols);
+  if (name == "head") return put(head, c.vocab, W, 0, data, c.vocab, name, rows, cols);
+  if (name == "final.norm") return put(final_norm, 1, W, 0, data, 1, name, rows, cols);
+  if (name.size() < 3 || name[0] != 'l') return fail("unknown tensor " + name);
+  const size_t dot = name.find('.');
+  if (dot == std::string::npos || dot < 2) return fail("unknown tensor " + name);
+  const int li = atoi(name.substr(1, dot - 1).c_str());
+  if (li < 0 || li >= c.n_layers) return fail("layer index out of range: " + name);
+  Layer& L = layers[li];
+  const LayerCfg& a = L.c;
+  const std::string sub = name.substr(dot + 1);
+  bool ok;
+  if (sub == "norm1") ok = put(L.norm1, 1, W, 0, data, 1, name, rows, cols);
+  else if (sub == "norm2") ok = put(L.norm2, 1, W, 0, data, 1, name, rows, cols);
+  else if (sub == "mix.q") ok = put(L.q, a.heads * (a.dim + a.rot_dim), W, 0, data, a.heads * (a.dim + a.rot_dim), name, rows, cols);
+  else if (sub == "mix.dkv" && a.kv_from < 0) ok = put(L.dkv, a.kv_rank + a.rot_dim, W, 0, data, a.kv_rank + a.rot_dim, name, rows, cols);
+  else if (sub == "mix.dkv.norm" && a.kv_from < 0) ok = put(L.dkv_norm, 1, a.kv_rank, 0, data, 1, name, rows, cols);
+  else if (sub == "mix.uk") ok = put(L.uk, a.heads * a.dim, a.kv_rank, 0, data, a.heads * a.dim, name, rows, cols);
+  else if (sub == "mix.uv") ok = put(L.uv, a.heads * a.vdim, a.kv_rank, 0, data, a.heads * a.vdim, name, rows, cols);
+  else if (sub == "mix.sink") ok = put(L.sink, 1, a.heads, 0, data, 1, name, rows, cols);
+  else if (sub == "mix.g") ok = put(L.g, a.heads, W, 0, data, a.heads, name, rows, cols);
+  else if (sub == "mix.o") ok = put(L.o, W, a.heads * a.vdim, 0, data, W, name, rows, cols);
+  else if (a.mlp_kind == 1 && sub == "mlp.gate") ok = put(L.gate_up, 2 * a.ff, W, 0, data, a.ff, name, rows, cols);
+  else if (a.mlp_kind == 1 && sub == "mlp.up") ok = put(L.gate_up, 2 * a.ff, W, a.ff, data, a.ff, name, rows, cols);
+  else if (a.mlp_kind == 1 && sub == "mlp.down") ok = put(L.down, W, a.ff, 0, data, W, name, rows, cols);
+  else if (a.mlp_kind == 2 && sub == "mlp.router") ok = put(L.router, a.experts, W, 0, data, a.experts, name, rows, cols);
+  else if (a.mlp_kind == 2 && a.shared_ff > 0 && sub == "mlp.shared.up") ok = put(L.s_up, a.shared_ff, W, 0, data, a.shared_ff, name, rows, cols);
+  else if (a.mlp_kind == 2 && a.shared_ff > 0 && sub == "mlp.shared.down") ok = put(L.s_down, W, a.shared_ff, 0, data, W, name, rows, cols);
+  else if (a.mlp_kind == 2 && a.shared_ff > 0 && sub == "mlp.shared.sg") ok = put(L.s_gate, 1, W, 0, data, 1, name, rows, cols);
+  else if (a.mlp_kind == 2 && sub.rfind("mlp.e", 0) == 0) {
+    const size_t d2 = sub.find('.', 5);
+    if (d2 == std::string::npos) return fail("unknown tensor " + name);
+    const int e = atoi(sub.substr(5, d2 - 5).c_str());
+    const std::string part = sub.substr(d2 + 1);
+    if (e < 0 || e >= a.experts) return fail("expert index out of range: " + name);
+    if (part == "up") ok = put(L.e_up, a.experts * a.expert_ff, W, e * a.expert_ff, data, a.expert_ff, name, rows, cols);
+    else if (part == "down") ok = put(L.e_down, a.experts * W, a.expert_ff, e * W, data, W, name, rows, cols);
+    else return fail("unknown tensor " + name);
+  } else {
+    return fail("unknown tensor " + name + " for the configuration of layer " + std::to_string(li));
+  }
+  if (ok) L.got.insert(sub);
+  return ok;
+}
+
+// angular frequency of every rotated pair; with YaRN scaling, pairs that turn fewer than `slow` times over the original
+// context are slowed by `factor`, pairs that turn more than `fast` times are kept, a linear ramp over the pair index blends
+static void rotary_table(const LayerCfg& a, std::vector<float>* f, float* mag) {
+  const int half = a.rot_dims / 2;
+  f->resize(std::max(half, 1));
+  *mag = 1.f;
+  double lo = 0, hi = 0;
+  if (a.has_scaling) {
+    auto pair_of = [&](double turns) { return a.rot_dims * std::log((double)a.s_original / (2.0 * M_PI * turns)) / (2.0 * std::log((double)a.rot_base)); };
+    lo = std::max(std::floor(pair_of(a.s_fast)), 0.0);
+    hi = std::min(std::ceil(pair_of(a.s_slow)), (double)a.rot_dims - 1.0);
+    *mag = (float)(0.1 * std::log((double)a.s_factor) + 1.0);
+  }
+  for (int i = 0; i < half; ++i) {
+    double w = std::pow((double)a.rot_base, -2.0 * i / a.rot_dims);
+    if (a.has_scaling) {
+      const double ramp = std::min(1.0, std::max(0.0, (i - lo) / std::max(hi - lo, 0.001)));
+      w = w / a.s_factor * ramp + w * (1.0 - ramp);
+    }
+    (*f)[i] = (float)w;
+  }
+}
+
+bool Model::finalize() {
+  if (!embed.d.ptr || !head.d.ptr || !final_norm.d.ptr) return fail("embed / head / final.norm missing");
+  for (int i = 0; i < c.n_layers; ++i) {
+    Layer& L = layers[i];
+    const LayerCfg& a = L.c;
+    std::vector<std::string> need = {"norm1", "mix.q", "mix.uk", "mix.uv", "mix.sink", "mix.g", "mix.o"};
+    if (a.kv_from < 0) need.insert(need.end(), {"mix.dkv", "mix.dkv.norm"});
+    if (a.mlp_kind) need.push_back("norm2");
+    if (a.mlp_kind == 1) need.insert(need.end(), {"mlp.gate", "mlp.up", "mlp.down"});
+    if (a.mlp_kind == 2) {
+      need.push_back("mlp.router");
+      for (int e = 0; e < a.experts; ++e) {
+        need.push_back("mlp.e" + std::to_string(e) + ".up");
+        need.push_back("mlp.e" + std::to_string(e) + ".down");
+      }
+      if (a.shared_ff > 0) need.insert(need.end(), {"mlp.shared.up", "mlp.shared.down", "mlp.shared.sg"});
+    }
+    for (auto& n : need)
+      if (!L.got.count(n)) return fail("tensor " + lname(i, n.c_str()) + " is missing");
+    std::vector<float> f;
+    rotary_table(a, &f, &L.mag);
+    if (!L.freq.alloc_zeros(f.size() * 4) || !cu(cudaMemcpy(L.freq.ptr, f.data(), f.size() * 4, cudaMemcpyHostToDevice), "rotary table"))
+      return fail("rotary table upload failed");
+  }
+  if (c.num_pages <= 0) {  // a share of what is free, as the other hosts size their pools
+    size_t fr = 0, tot = 0;
+    cudaMemGetInfo(&fr, &tot);
+    c.num_pages = (int)std::min<size_t>((size_t)(fr * 0.85) / ((size_t)page_stride * es), (size_t)1 << 20);
+  }
+  c.num_pages += 1;  // page 0 is never handed out (padding rows of captured steps point there)
+  if (!cache.alloc_zeros((size_t)c.num_pages * page_stride * es)) return fail("cache pool allocation failed");
+  pool.init(c.num_pages);
+  std::vector<int> pad;
+  pool.acquire(1, &pad);
+  reqs.assign(c.max_requests, pq::KvState());
+  if (cudaMallocHost((void**)&sampled_h, 4096) != cudaSuccess) return fail("pinned allocation failed");
+  if (!top1_val.alloc_zeros(64) || !top1_states.alloc_zeros(1 << 16)) return fail("sampler scratch allocation failed");
+  finalized = true;
+  return cu(cudaStreamSynchronize(st), "finalize");
+}
+
+bool Model::ensure_scratch(int T, int R) {
+  bool ok = true;
+  if (T > cap_t) {
+    cudaStreamSynchronize(st);
+    const size_t n = ((size_t)T + 63) / 64 * 64, W = c.width;
+    ok = x.alloc_uninit(n * W * 4) && xa.alloc_uninit(n * W * es) && q.alloc_uninit(n * mx_q * es) && dkv.alloc_uninit(n * mx_dkv * es) &&
+         qa.alloc_uninit(n * mx_qa * es) && gate.alloc_uninit(n * mx_h * 4) && olat.alloc_uninit(n * mx_olat * es) &&
+         ao.alloc_uninit(n * mx_ao * es) && mix.alloc_uninit(n * W * es) && gu.alloc_uninit(n * std::max(mx_gu, 1) * es) &&
+         act.alloc_uninit(n * std::max(mx_act, 1) * es) && z.alloc_uninit(n * std::max(mx_e, 1) * 4) && ids.alloc_uninit(n * std::max(mx_top, 1) * 4) &&
+         wts.alloc_uninit(n * std::max(mx_top, 1) * 4) && hid.alloc_uninit(n * std::max(mx_hid, 1) * es) && yf.alloc_uninit(n * W * 4) &&
+         sgl.alloc_uninit(n * 4) && sh.alloc_uninit(n * W * es);
+    if (ok) cap_t = (int)n;
+  }
+  if (ok && R > cap_r) {
+    cudaStreamSynchronize(st);
+    const size_t n = ((size_t)R + 15) / 16 * 16;
+    ok = xr.alloc_uninit(n * c.width * es) && logits_e.alloc_uninit(n * c.vocab * es) && logits_f.alloc_uninit(n * c.vocab * 4) &&
+         logits_bf.alloc_uninit(n * c.vocab * 2) && sampled_d.alloc_zeros(n * 4);
+    if (ok) cap_r = (int)n;
+  }
+  return ok ? true : fail("scratch allocation failed");
+}
+
+// Y[N, W.rows] = X[N, W.cols] W^T: the library's tensor-core GEMM / streaming GEMV in bf16, plain FMA in fp32
+bool Model::lin(const Mat& W, const void* X, void* Y, int N) {
+  if (c.f32)
+    return rc(k.pk_gemm_strided(X, W.d.ptr, Y, nullptr, N, W.rows, W.cols, W.cols, 1, W.cols, W.rows, 1, 0, 0, 0, 0, 0, 1, st), "linear layer");
+  k.gemm_cuda((const pk_bf16*)W.d.ptr, (const pk_bf16*)X, (pk_bf16*)Y, W.rows, N, W.cols, st);
+  return true;
+}
+
+bool Model::run_layer(int li, int T, const int* d_pos, const int* d_req, const int* d_poff, const int* d_pages) {
+  Layer& L = layers[li];
+  const LayerCfg& a = L.c;
+  const int W = c.width, f32 = c.f32, H = a.heads, r = a.kv_rank, rd = a.rot_dim, D = r + rd;
+  char* pool_base = (char*)cache.ptr + (size_t)L.cache_off * es;
+  // ---- mixer
+  if (!lin(L.q, xa.ptr, q.ptr, T)) return false;
+  if (a.kv_from < 0) {
+    if (!lin(L.dkv, xa.ptr, dkv.ptr, T)) return false;
+    if (!rc(k.pk_latent_kv_append(dkv.ptr, L.dkv_norm.d.ptr, d_pos, d_req, d_poff, d_pages, pool_base, page_stride, c.page_size, r, rd, a.rot_dims,
+                                  (const float*)L.freq.ptr, L.mag, c.eps, T, f32, st),
+            "latent cache append"))
+      return false;
+  }
+  // fold the unrotated query onto the latent (per head: qa[:, :r] = q_unrotated W_uk[h]), rotate the other part beside it
+  if (!rc(k.pk_gemm_strided(q.ptr, L.uk.d.ptr, qa.ptr, nullptr, T, r, a.dim, (long)H * (a.dim + rd), r, 1, (long)H * D, H, a.dim + rd, (long)a.dim * r,
+                            D, 0, 0, f32, st),
+          "query fold"))
+    return false;
+  if (rd > 0 && !rc(k.pk_rope_slice(q.ptr, qa.ptr, d_pos, (const float*)L.freq.ptr, L.mag, T, H, a.dim + rd, a.dim, D, r, rd, a.rot_dims, f32, st),
+                    "query rotation"))
+    return false;
+  if (!rc(k.pk_res32_skinny_proj(L.g.d.ptr, (const float*)x.ptr, (float*)gate.ptr, H, W, T, f32, st), "output gate")) return false;
+  if (!rc(k.pk_latent_attention(qa.ptr, pool_base, L.sink.d.ptr, d_pos, d_req, d_poff, d_pages, olat.ptr, page_stride, c.page_size, T, H, r, rd,
+                                a.scale, f32, st),
+          "latent attention"))
+    return false;
+  // values: ao[:, h] = logistic(gate[:, h]) * (o_lat[:, h] W_uv[h]^T)
+  if (!rc(k.pk_gemm_strided(olat.ptr, L.uv.d.ptr, ao.ptr, (const float*)gate.ptr, T, a.vdim, r, (long)H * r, 1, r, (long)H * a.vdim, H, r,
+                            (long)a.vdim * r, a.vdim, H, 2, f32, st),
+          "value expansion"))
+    return false;
+  if (!lin(L.o, ao.ptr, mix.ptr, T)) return false;
+  if (!rc(k.pk_res32_offset_norm_add(mix.ptr, f32, L.norm1.d.ptr, (float*)x.ptr, xa.ptr, W, T, c.eps, f32, st), "norm1")) return false;
+  // ---- feed-forward
+  if (a.mlp_kind == 1) {
+    if (!lin(L.gate_up, xa.ptr, gu.ptr, T)) return false;
+    if (!rc(k.pk_act(gu.ptr, act.ptr, a.ff, T, 0, f32, st), "SwiGLU")) return false;
+    if (!lin(L.down, act.ptr, mix.ptr, T)) return false;
+    if (!rc(k.pk_res32_offset_norm_add(mix.ptr, f32, L.norm2.d.ptr, (float*)x.ptr, xa.ptr, W, T, c.eps, f32, st), "norm2")) return false;
+  } else if (a.mlp_kind == 2) {
+    if (!rc(k.pk_res32_skinny_proj(L.router.d.ptr, (const float*)x.ptr, (float*)z.ptr, a.experts, W, T, f32, st), "router")) return false;
+    if (!rc(k.pk_router_grouped_topk((const float*)z.ptr, (int*)ids.ptr, (float*)wts.ptr, T, a.experts, a.top, a.groups, a.keep, a.route_scale, st),
+            "router top-k"))
+      return false;
+    if (!rc(k.pk_moe_up_relu2(xa.ptr, L.e_up.d.ptr, (const int*)ids.ptr, hid.ptr, T, a.top, W, a.expert_ff, f32, st), "experts up")) return false;
+    const void* shared = nullptr;
+    if (a.shared_ff > 0) {
+      if (!lin(L.s_up, xa.ptr, gu.ptr, T)) return false;
+      if (!rc(k.pk_act(gu.ptr, act.ptr, a.shared_ff, T, 1, f32, st), "shared expert activation")) return false;
+      if (!lin(L.s_down, act.ptr, sh.ptr, T)) return false;
+      if (!rc(k.pk_res32_skinny_proj(L.s_gate.d.ptr, (const float*)x.ptr, (float*)sgl.ptr, 1, W, T, f32, st), "shared expert gate")) return false;
+      shared = sh.ptr;
+    }
+    if (!rc(k.pk_moe_down_combine(hid.ptr, L.e_down.d.ptr, (const int*)ids.ptr, (const float*)wts.ptr, shared, (const float*)sgl.ptr, (float*)yf.ptr, T,
+                                  a.top, W, a.expert_ff, f32, st),
+            "experts down"))
+      return false;
+    if (!rc(k.pk_res32_offset_norm_add(yf.ptr, 1, L.norm2.d.ptr, (float*)x.ptr, xa.ptr, W, T, c.eps, f32, st), "norm2")) return false;
+  }
+  if (keep_trail)
+    return cu(cudaMemcpyAsync((char*)trail.ptr + (size_t)li * T * W * 4, x.ptr, (size_t)T * W * 4, cudaMemcpyDeviceToDevice, st), "trail copy");
+  return true;
+}
+
+// One engine step over a ragged batch.  tokens: all entries' tokens back to back; lens[i] tokens belong to request rids[i];
+// rows: indices into that flat token list whose logits are wanted.  Leaves fp32 logits [n_rows, vocab] in logits_f (and the
+// greedy token of each row in sampled_h when want_sample).
+bool Model::step(int n, const int* tokens, const int* lens, const int* rids, int n_rows, const int* rows, int want_sample) {
+  if (!finalized) return fail("model not finalized");
+  if (n <= 0) return fail("empty step");
+  int T = 0, pages_needed = 0;
+  for (int i = 0; i < n; ++i) {
+    if (rids[i] < 0 || rids[i] >= (int)reqs.size() || !reqs[rids[i]].live) return fail("bad request id");
+    for (int j = 0; j < i; ++j)
+      if (rids[j] == rids[i]) return fail("a request appears twice in one step");
+    if (lens[i] <= 0) return fail("an entry without tokens");
+    const pq::KvState& s = reqs[rids[i]];
+    pages_needed += std::max(0, (s.seq_len + lens[i] + c.page_size - 1) / c.page_size - (int)s.pages.size());
+    T += lens[i];
+  }
+  for (int t = 0; t < T; ++t)
+    if (tokens[t] < 0 || tokens[t] >= c.vocab) return fail("token id outside the vocabulary");
+  for (int i = 0; i < n_rows; ++i)
+    if (rows[i] < 0 || rows[i] >= T) return fail("logits row outside the step");
+  if (pages_needed > (int)pool.free_list.size()) {
+    char b[128];
+    snprintf(b, sizeof b, "cache pool: out of pages (need %d more, %d available)", pages_needed, (int)pool.free_list.size());
+    return fail(b);
+  }
+  if (!ensure_scratch(T, std::max(n_rows, 1))) return false;
+  if (keep_trail && !trail.alloc_uninit((size_t)c.n_layers * T * c.width * 4)) return fail("trail allocation failed");
+  trail_tokens = T;
+  struct Txn {  // undo record: a failure below gives back the pages and the lengths of this step
+    Model* m;
+    std::vector<std::pair<int, std::pair<int, size_t>>> old;
+    bool committed = false;
+    ~Txn() {
+      if (committed) return;
+      for (auto& o : old) {
+        pq::KvState& s = m->reqs[o.first];
+        std::vector<int> extra(s.pages.begin() + o.second.second, s.pages.end());
+        m->pool.release(extra);
+        s.pages.resize(o.second.second);
+        s.seq_len = o.second.first;
+      }
+    }
+  } txn{this, {}, false};
+  // metadata block: [tok T][pos T][req T][page_off n][rows R][pages ...]
+  std::vector<int> meta((size_t)3 * T + n + n_rows);
+  int t0 = 0;
+  std::vector<int> page_list;
+  for (int i = 0; i < n; ++i) {
+    pq::KvState& s = reqs[rids[i]];
+    txn.old.push_back({rids[i], {s.seq_len, s.pages.size()}});
+    const int need = (s.seq_len + lens[i] + c.page_size - 1) / c.page_size - (int)s.pages.size();
+    if (need > 0 && !pool.acquire(need, &s.pages)) return fail("cache pool: out of pages");
+    for (int t = 0; t < lens[i]; ++t) {
+      meta[t0 + t] = tokens[t0 + t];
+      meta[T + t0 + t] = s.seq_len + t;
+      meta[2 * T + t0 + t] = i;
+    }
+    meta[3 * T + i] = (int)page_list.size();
+    page_list.insert(page_list.end(), s.pages.begin(), s.pages.end());
+    s.seq_len += lens[i];
+    t0 += lens[i];
+  }
+  for (int i = 0; i < n_rows; ++i) meta[3 * T + n + i] = rows[i];
+  meta.insert(meta.end(), page_list.begin(), page_list.end());
+  if (meta.size() > meta_cap) {
+    cudaStreamSynchronize(st);
+    if (meta_h) cudaFreeHost(meta_h);
+    meta_cap = meta.size() * 2 + 1024;
+    if (cudaMallocHost((void**)&meta_h, meta_cap * 4) != cudaSuccess || !meta_d.alloc_uninit(meta_cap * 4)) {
+      meta_h = nullptr;
+      meta_cap = 0;
+      return fail("metadata allocation failed");
+    }
+  }
+  memcpy(meta_h, meta.data(), meta.size() * 4);
+  if (!cu(cudaMemcpyAsync(meta_d.ptr, meta_h, meta.size() * 4, cudaMemcpyHostToDevice, st), "metadata upload")) return false;
+  const int* M = meta_d.i32();
+  const int *d_tok = M, *d_pos = M + T, *d_req = M + 2 * T, *d_poff = M + 3 * T, *d_rows = M + 3 * T + n, *d_pages = M + 3 * T + n + n_rows;
+  if (!rc(k.pk_res32_embed(embed.d.ptr, d_tok, (float*)x.ptr, xa.ptr, c.width, T, c.f32, st), "embedding")) return false;
+  for (int li = 0; li < c.n_layers; ++li)
+    if (!run_layer(li, T, d_pos, d_req, d_poff, d_pages)) return false;
+  if (n_rows > 0) {
+    if (!rc(k.pk_res32_offset_norm_rows((const float*)x.ptr, d_rows, final_norm.d.ptr, xr.ptr, c.width, n_rows, c.eps, c.f32, st), "final norm"))
+      return false;
+    if (!lin(head, xr.ptr, logits_e.ptr, n_rows)) return false;
+    if (!rc(k.pk_convert(logits_e.ptr, c.f32, logits_f.ptr, 1, (long)n_rows * c.vocab, st), "logits")) return false;
+    if (want_sample) {
+      const pk_bf16* lb = (const pk_bf16*)logits_e.ptr;
+      if (c.f32) {
+        if (!rc(k.pk_convert(logits_e.ptr, 1, logits_bf.ptr, 0, (long)n_rows * c.vocab, st), "logits")) return false;
+        lb = (const pk_bf16*)logits_bf.ptr;
+      }
+      for (int i = 0; i < n_rows; ++i)
+        k.flashinfer_top1_cuda(lb + (size_t)i * c.vocab, (pk_bf16*)top1_val.ptr, (uint8_t*)top1_states.ptr, sampled_d.i32() + i, c.vocab, st);
+      if (!cu(cudaMemcpyAsync(sampled_h, sampled_d.ptr, (size_t)std::min(n_rows, 1024) * 4, cudaMemcpyDeviceToHost, st), "sampled tokens")) return false;
+    }
+  }
+  if (!cu(cudaStreamSynchronize(st), "step")) return false;
+  txn.committed = true;
+  return true;
+}
+
+}  // namespace pv
+
+extern "C" {
+
+static thread_local std::string g_pv_err;
+#define PV_API __attribute__((visibility("default")))
+#define PV_M static_cast<pv::Model*>(mp)
+
+PV_API const char* pv_create_error() { return g_pv_err.c_str(); }
+
+PV_API void* pv_create(const pv::ModelCfg* mc, const pv::LayerCfg* lc, const char* kernel_lib_path) {
+  auto* m = new pv::Model();
+  auto bail = [&](const std::string& e) -> void* {
+    g_pv_err = e;
+    delete m;
+    return nullptr;
+  };
+  if (!m->configure(*mc, lc)) return bail(m->err);
+  std::string e = m->k.load(kernel_lib_path);
+  if (!e.empty()) return bail(e);
+  if (m->k.cuda_set_device(mc->device) != 0) return bail("cuda_set_device failed (no CUDA device?)");
+  if (cudaStreamCreateWithFlags(&m->st, cudaStreamNonBlocking) != cudaSuccess)
+    return bail(std::string("stream creation failed: ") + cudaGetErrorString(cudaGetLastError()));
+  m->k.cublas_init();
+  m->k.pk_b200_set_pdl(mc->enable_pdl);
+  g_pv_err.clear();
+  return m;
+}
+PV_API void pv_destroy(void* mp) { delete PV_M; }
+PV_API const char* pv_last_error(void* mp) { return PV_M->err.c_str(); }
+PV_API int pv_load_tensor(void* mp, const char* name, const void* data, int rows, int cols, int is_f32) {
+  return PV_M->load_tensor(name, data, rows, cols, is_f32) ? 0 : -1;
+}
+PV_API int pv_finalize(void* mp) { return PV_M->finalize() ? 0 : -1; }
+PV_API int pv_request_alloc(void* mp) {
+  auto& v = PV_M->reqs;
+  for (size_t i = 0; i < v.size(); ++i)
+    if (!v[i].live) {
+      v[i] = pq::KvState();
+      v[i].live = true;
+      return (int)i;
+    }
+  PV_M->err = "every request slot is in use";
+  return -1;
+}
+PV_API void pv_request_free(void* mp, int id) {
+  auto& v = PV_M->reqs;
+  if (id < 0 || id >= (int)v.size() || !v[id].live) return;
+  PV_M->pool.release(v[id].pages);
+  v[id] = pq::KvState();
+}
+PV_API int pv_seq_len(void* mp, int id) {
+  auto& v = PV_M->reqs;
+  return (id < 0 || id >= (int)v.size() || !v[id].live) ? -1 : v[id].seq_len;
+}
+PV_API int pv_available_pages(void* mp) { return (int)PV_M->pool.free_list.size(); }
+PV_API int pv_page_size(void* mp) { return PV_M->c.page_size; }
+// the pages a request holds, in order (tests check that freed pages are handed out again)
+PV_API int pv_request_pages(void* mp, int id, int* out, int cap) {
+  auto& v = PV_M->reqs;
+  if (id < 0 || id >= (int)v.size() || !v[id].live) return -1;
+  const int n = (int)v[id].pages.size();
+  for (int i = 0; i < std::min(n, cap); ++i) out[i] = v[id].pages[i];
+  return n;
+}
+PV_API int pv_step(void* mp, int n, const int* tokens, const int* lens, const int* rids, int n_rows, const int* rows, int want_sample,
+                   float* logits_host, int* sampled) {
+  pv::Model* m = PV_M;
+  if (!m->step(n, tokens, lens, rids, n_rows, rows, want_sample)) return -1;
+  if (n_rows > 0 && logits_host &&
+      cudaMemcpy(logits_host, m->logits_f.ptr, (size_t)n_rows * m->c.vocab * 4, cudaMemcpyDeviceToHost) != cudaSuccess) {
+    m->err = "logits copy failed";
+    return -1;
+  }
+  if (want_sample && sampled)
+    for (int i = 0; i < std::min(n_rows, 1024); ++i) sampled[i] = m->sampled_h[i];
+  return 0;
+}
+PV_API void pv_keep_trail(void* mp, int on) { PV_M->keep_trail = on != 0; }
+// residual stream after every layer of the last step, [layers, tokens, width] fp32
+PV_API int pv_copy_trail(void* mp, float* host_out) {
+  pv::Model* m = PV_M;
+  if (!m->keep_trail || !m->trail.ptr) return -1;
+  return cudaMemcpy(host_out, m->trail.ptr, (size_t)m->c.n_layers * m->trail_tokens * m->c.width * 4, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -1;
+}
+PV_API int64_t pv_launch_count(void* mp, int reset) { return PV_M->k.pk_b200_launch_count(reset); }
+
+// greedy generation of one request, timed like the other hosts' generate: first token after the whole prompt, then one step per token
+PV_API int pv_generate(void* mp, const int* prompt, int n_prompt, int max_tokens, int* out, double* ttft_ms, double* step_ms) {
+  pv::Model* m = PV_M;
+  const int rid = pv_request_alloc(mp);
+  if (rid < 0) return -1;
+  using clk = std::chrono::steady_clock;
+  auto t0 = clk::now();
+  int row = n_prompt - 1, len = n_prompt, ok = 1;
+  if (!m->step(1, prompt, &len, &rid, 1, &row, 1)) ok = 0;
+  if (ok) {
+    out[0] = m->sampled_h[0];
+    *ttft_ms = std::chrono::duration<double, std::milli>(clk::now() - t0).count();
+    for (int i = 1; i < max_tokens && ok; ++i) {
+      auto t1 = clk::now();
+      int one = 1, zero = 0, tok = out[i - 1];
+      if (!m->step(1, &tok, &one, &rid, 1, &zero, 1)) ok = 0;
+      else out[i] = m->sampled_h[0];
+      step_ms[i - 1] = std::chrono::duration<double, std::milli>(clk::now() - t1).count();
+    }
+  }
+  pv_request_free(mp, rid);
+  return ok ? 0 : -1;
+}
+}

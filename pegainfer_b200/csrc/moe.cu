@@ -1,0 +1,180 @@
+// Mixture-of-experts feed-forward: group-limited top-k routing over softmax scores, and the chosen experts' two-matrix
+// feed-forward (up -> activation -> down) gathered per token, plus an optional always-on shared expert that enters
+// through a per-token logistic gate.
+//   router: s = softmax(z) over all experts (fp32); experts are split into `groups` equal runs of neighbours, a group
+//           scores as its best expert, only the `keep` best groups stay eligible; the `top` best eligible experts are
+//           chosen (lowest index wins ties); weight = s / (sum of chosen s + 1e-20) * scale.
+//   experts: hid[t,k,:] = act(W_up[e_k] x_t);  y[t] = sum_k w_k W_down[e_k] hid[t,k,:]  (+ logistic(g_t) * shared[t]).
+// The per-token form reads only the chosen experts' weights: the decode path (a few tokens) is bound by those bytes.
+#include "common.cuh"
+#include "typed.cuh"
+
+namespace pk {
+
+// (value, index) arg-max over a warp, lowest index on ties
+__device__ __forceinline__ void warp_argmax(float& v, int& i) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+    if (ov > v || (ov == v && oi < i)) {
+      v = ov;
+      i = oi;
+    }
+  }
+}
+
+// one warp per token; shared memory: scores [E] + group eligibility [groups]
+__global__ void router_grouped_topk_kernel(const float* __restrict__ z, int* __restrict__ ids, float* __restrict__ wts, int E, int top,
+                                           int groups, int keep, float scale) {
+  extern __shared__ float sm[];
+  pdl_wait();
+  const int t = blockIdx.x, lane = threadIdx.x;
+  float* s = sm;            // [E]
+  float* gs = s + E;        // [groups] group score, -1 once taken
+  float* ok = gs + groups;  // [groups] 1 = eligible
+  const float* zr = z + (size_t)t * E;
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, zr[e]);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) {
+    const float v = expf(zr[e] - mx);
+    s[e] = v;
+    sum += v;
+  }
+  sum = warp_sum(sum);
+  const float inv = 1.f / sum;
+  __syncwarp();
+  for (int e = lane; e < E; e += 32) s[e] *= inv;
+  __syncwarp();
+  const int per = E / groups;
+  for (int g = lane; g < groups; g += 32) {
+    float b = -1.f;
+    for (int e = 0; e < per; ++e) b = fmaxf(b, s[g * per + e]);
+    gs[g] = b;
+    ok[g] = 0.f;
+  }
+  __syncwarp();
+  for (int r = 0; r < keep; ++r) {
+    float bv = -2.f;
+    int bi = 0x7fffffff;
+    for (int g = lane; g < groups; g += 32)
+      if (gs[g] > bv) {
+        bv = gs[g];
+        bi = g;
+      }
+    warp_argmax(bv, bi);
+    if (lane == 0) {
+      gs[bi] = -3.f;
+      ok[bi] = 1.f;
+    }
+    __syncwarp();
+  }
+  float total = 0.f;
+  for (int r = 0; r < top; ++r) {
+    float bv = -2.f;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32)
+      if (ok[e / per] > 0.f && s[e] > bv) {
+        bv = s[e];
+        bi = e;
+      }
+    warp_argmax(bv, bi);
+    total += bv;
+    if (lane == 0) {
+      ids[(size_t)t * top + r] = bi;
+      wts[(size_t)t * top + r] = bv;
+      s[bi] = -4.f;  // taken
+    }
+    __syncwarp();
+  }
+  if (lane < top) wts[(size_t)t * top + lane] = wts[(size_t)t * top + lane] / (total + 1e-20f) * scale;
+}
+
+// hid[t, k, f] = act(W_up[ids[t,k]][f] . x[t]); act = relu^2.  One block per (token, choice).
+template <typename E>
+__global__ void moe_up_kernel(const E* __restrict__ xa, const E* __restrict__ w_up, const int* __restrict__ ids, E* __restrict__ hid, int width,
+                              int ff) {
+  extern __shared__ float xs[];
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int tok = blockIdx.x, k = blockIdx.y, top = gridDim.y;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) xs[i] = to_f(xa[(size_t)tok * width + i]);
+  __syncthreads();
+  const E* W = w_up + (size_t)ids[(size_t)tok * top + k] * ff * width;
+  for (int f = warp; f < ff; f += nw) {
+    const E* wr = W + (size_t)f * width;
+    float acc = 0.f;
+    for (int i = lane; i < width; i += 32) acc = fmaf(to_f(wr[i]), xs[i], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      const float u = fmaxf(acc, 0.f);
+      hid[((size_t)tok * top + k) * ff + f] = from_f<E>(u * u);
+    }
+  }
+}
+
+// y[t][i] = sum_k wts[t,k] * (W_down[ids[t,k]][i] . hid[t,k]) + logistic(sg[t]) * shared[t][i]; fp32 out.  One block per token.
+template <typename E>
+__global__ void moe_down_kernel(const E* __restrict__ hid, const E* __restrict__ w_down, const int* __restrict__ ids, const float* __restrict__ wts,
+                                const E* __restrict__ shared, const float* __restrict__ sg, float* __restrict__ y, int width, int ff, int top) {
+  extern __shared__ float hs[];  // [top][ff]
+  pdl_wait();
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < top * ff; i += blockDim.x) hs[i] = to_f(hid[(size_t)t * top * ff + i]);
+  __syncthreads();
+  const float g = shared ? 1.f / (1.f + expf(-sg[t])) : 0.f;
+  for (int i = warp; i < width; i += nw) {
+    float tot = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const E* wr = w_down + ((size_t)ids[(size_t)t * top + k] * width + i) * ff;
+      float acc = 0.f;
+      for (int f = lane; f < ff; f += 32) acc = fmaf(to_f(wr[f]), hs[k * ff + f], acc);
+      tot = fmaf(wts[(size_t)t * top + k], warp_sum(acc), tot);
+    }
+    if (lane == 0) y[(size_t)t * width + i] = tot + (shared ? g * to_f(shared[(size_t)t * width + i]) : 0.f);
+  }
+}
+
+}  // namespace pk
+
+using namespace pk;
+
+extern "C" int pk_router_grouped_topk(const float* logits, int* ids, float* weights, int tokens, int experts, int top, int groups, int keep,
+                                      float scale, pk_stream st) {
+  if (!logits || !ids || !weights || tokens <= 0 || experts <= 0 || top <= 0 || top > 32 || groups <= 0 || experts % groups || keep <= 0 ||
+      keep > groups || top > keep * (experts / groups))
+    return -1;
+  launch(router_grouped_topk_kernel, dim3(tokens), dim3(32), (size_t)(experts + 2 * groups) * sizeof(float), st, true, logits, ids, weights, experts,
+         top, groups, keep, scale);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int pk_moe_up_relu2(const void* xa, const void* w_up, const int* ids, void* hid, int tokens, int top, int width, int ff, int f32,
+                               pk_stream st) {
+  if (!xa || !w_up || !ids || !hid || tokens <= 0 || top <= 0 || width <= 0 || ff <= 0) return -1;
+  const size_t smem = (size_t)width * sizeof(float);
+  if (f32)
+    launch(moe_up_kernel<float>, dim3(tokens, top), dim3(256), smem, st, true, (const float*)xa, (const float*)w_up, ids, (float*)hid, width, ff);
+  else
+    launch(moe_up_kernel<bf16>, dim3(tokens, top), dim3(256), smem, st, true, (const bf16*)xa, (const bf16*)w_up, ids, (bf16*)hid, width, ff);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int pk_moe_down_combine(const void* hid, const void* w_down, const int* ids, const float* weights, const void* shared,
+                                   const float* shared_gate, float* y, int tokens, int top, int width, int ff, int f32, pk_stream st) {
+  if (!hid || !w_down || !ids || !weights || !y || tokens <= 0 || top <= 0 || width <= 0 || ff <= 0 || (shared && !shared_gate)) return -1;
+  const size_t smem = (size_t)top * ff * sizeof(float);
+  if (smem > 200 * 1024) return -2;
+  if (f32) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_down_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch(moe_down_kernel<float>, dim3(tokens), dim3(256), smem, st, true, (const float*)hid, (const float*)w_down, ids, weights,
+           (const float*)shared, shared_gate, y, width, ff, top);
+  } else {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_down_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch(moe_down_kernel<bf16>, dim3(tokens), dim3(256), smem, st, true, (const bf16*)hid, (const bf16*)w_down, ids, weights, (const bf16*)shared,
+           shared_gate, y, width, ff, top);
+  }
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,250 @@
+// Ops for models that keep an fp32 residual stream and norm the OUTPUT of a sublayer (x <- x + norm(f(x))):
+// embedding into fp32, RMS norm with a weight stored as an offset from one fused with the residual add and the cast that
+// feeds the next projection, final norm over gathered rows, a skinny fp32 projection (routers, gates), activations, and
+// a strided batched GEMM in plain FMA arithmetic (true fp32 when the element type is float; per-head factor products of
+// the latent attention in either type).  Every kernel is templated on the activation / weight element type E
+// (bf16 or float); arithmetic is fp32 throughout and a value is rounded once, when it is stored as E.
+// All of these are HBM-bound except the GEMM: 4 - 12 bytes per element per pass.
+#include "common.cuh"
+#include "typed.cuh"
+
+namespace pk {
+
+template <typename E>
+__global__ void embed_res32_kernel(const E* __restrict__ embed, const int* __restrict__ tok, float* __restrict__ x,
+                                   E* __restrict__ xa, int width) {
+  pdl_wait();
+  const int t = blockIdx.x;
+  const E* row = embed + (size_t)tok[t] * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const E v = row[i];
+    x[(size_t)t * width + i] = to_f(v);
+    xa[(size_t)t * width + i] = v;
+  }
+}
+
+// x[t] += y[t] / sqrt(mean(y[t]^2) + eps) * (1 + w);  xa[t] = E(x[t]).  Y is E or float.
+template <typename E, typename Y>
+__global__ void offset_norm_residual_kernel(const Y* __restrict__ y, const E* __restrict__ w, float* __restrict__ x,
+                                            E* __restrict__ xa, int width, float eps) {
+  __shared__ float red[33];
+  pdl_wait();
+  const int t = blockIdx.x;
+  const Y* yr = y + (size_t)t * width;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float v = to_f(yr[i]);
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)width + eps);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float r = x[(size_t)t * width + i] + to_f(yr[i]) * inv * (1.f + to_f(w[i]));
+    x[(size_t)t * width + i] = r;
+    xa[(size_t)t * width + i] = from_f<E>(r);
+  }
+}
+
+// out[r] = E(x[rows[r]] / rms * (1 + w)): the model's last norm, only for the rows whose logits are wanted
+template <typename E>
+__global__ void offset_norm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows, const E* __restrict__ w,
+                                        E* __restrict__ out, int width, float eps) {
+  __shared__ float red[33];
+  pdl_wait();
+  const float* xr = x + (size_t)rows[blockIdx.x] * width;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) ss += xr[i] * xr[i];
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)width + eps);
+  for (int i = threadIdx.x; i < width; i += blockDim.x)
+    out[(size_t)blockIdx.x * width + i] = from_f<E>(xr[i] * inv * (1.f + to_f(w[i])));
+}
+
+// out[t][m] = sum_k W[m][k] x[t][k] with the fp32 residual as input: one warp per output
+template <typename E>
+__global__ void skinny_proj_kernel(const E* __restrict__ W, const float* __restrict__ x, float* __restrict__ out, int M, int K) {
+  pdl_wait();
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const float* xr = x + (size_t)t * K;
+  for (int m = warp; m < M; m += nw) {
+    const E* wr = W + (size_t)m * K;
+    float acc = 0.f;
+    for (int k = lane; k < K; k += 32) acc = fmaf(to_f(wr[k]), xr[k], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) out[(size_t)t * M + m] = acc;
+  }
+}
+
+// kind 0: out[t][f] = silu(in[t][f]) * in[t][F + f]   (in is [T, 2F]: gate rows stacked over up rows)
+// kind 1: out[t][f] = relu(in[t][f])^2                (in is [T, F])
+template <typename E>
+__global__ void act_kernel(const E* __restrict__ in, E* __restrict__ out, int F, long total, int kind) {
+  pdl_wait();
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long t = i / F, f = i % F;
+    float r;
+    if (kind == 0) {
+      const float g = to_f(in[t * 2 * F + f]), u = to_f(in[t * 2 * F + F + f]);
+      r = g / (1.f + expf(-g)) * u;
+    } else {
+      const float u = fmaxf(to_f(in[i]), 0.f);
+      r = u * u;
+    }
+    out[i] = from_f<E>(r);
+  }
+}
+
+template <typename A, typename B>
+__global__ void convert_kernel(const A* __restrict__ in, B* __restrict__ out, long n) {
+  pdl_wait();
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) out[i] = from_f<B>(to_f(in[i]));
+}
+
+// C[b][i][j] = (sum_k A[b*bsA + i*lda + k] * B[b*bsB + k*sbk + j*sbn]) * f(row_scale[i*ld_scale + b])
+// f = identity (scale_kind 1) or logistic (scale_kind 2); no scale when row_scale is null.  64 x 64 output tile, 256 threads, 4 x 4 each.
+template <typename E>
+__global__ void gemm_strided_kernel(const E* __restrict__ A, const E* __restrict__ B, E* __restrict__ C, const float* __restrict__ row_scale,
+                                    int rows, int cols, int K, long lda, long sbk, long sbn, long ldc, long bsA, long bsB, long bsC,
+                                    int ld_scale, int scale_kind) {
+  constexpr int TL = 64, KT = 16;
+  __shared__ float as[KT][TL + 1], bs[KT][TL + 1];
+  pdl_wait();
+  const int b = blockIdx.z;
+  A += (size_t)b * bsA;
+  B += (size_t)b * bsB;
+  C += (size_t)b * bsC;
+  const int i0 = blockIdx.y * TL, j0 = blockIdx.x * TL;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < K; k0 += KT) {
+    for (int e = threadIdx.x; e < TL * KT; e += 256) {
+      const int r = e / KT, c = e % KT;  // consecutive threads walk k: contiguous for A (and for B when sbk == 1)
+      as[c][r] = (i0 + r < rows && k0 + c < K) ? to_f(A[(size_t)(i0 + r) * lda + k0 + c]) : 0.f;
+    }
+    if (sbk == 1) {
+      for (int e = threadIdx.x; e < TL * KT; e += 256) {
+        const int r = e / KT, c = e % KT;
+        bs[c][r] = (j0 + r < cols && k0 + c < K) ? to_f(B[(size_t)(j0 + r) * sbn + k0 + c]) : 0.f;
+      }
+    } else {
+      for (int e = threadIdx.x; e < TL * KT; e += 256) {
+        const int c = e / TL, r = e % TL;  // consecutive threads walk j
+        bs[c][r] = (j0 + r < cols && k0 + c < K) ? to_f(B[(size_t)(k0 + c) * sbk + (size_t)(j0 + r) * sbn]) : 0.f;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int c = 0; c < KT; ++c) {
+      float av[4], bv[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        av[u] = as[c][ty * 4 + u];
+        bv[u] = bs[c][tx * 4 + u];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int v = 0; v < 4; ++v) acc[u][v] = fmaf(av[u], bv[v], acc[u][v]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int i = i0 + ty * 4 + u;
+    if (i >= rows) continue;
+    float s = 1.f;
+    if (row_scale) {
+      s = row_scale[(size_t)i * ld_scale + b];
+      if (scale_kind == 2) s = 1.f / (1.f + expf(-s));
+    }
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const int j = j0 + tx * 4 + v;
+      if (j < cols) C[(size_t)i * ldc + j] = from_f<E>(acc[u][v] * s);
+    }
+  }
+}
+
+static inline int grid_1d(long n, int block) {
+  long g = (n + block - 1) / block;
+  return (int)(g < 1 ? 1 : (g > 148 * 16 ? 148 * 16 : g));
+}
+
+}  // namespace pk
+
+using namespace pk;
+
+#define PK_BY_TYPE(f32, CALL_F, CALL_B) \
+  do {                                  \
+    if (f32) {                          \
+      CALL_F;                           \
+    } else {                            \
+      CALL_B;                           \
+    }                                   \
+  } while (0)
+
+extern "C" int pk_res32_embed(const void* embed, const int* token_ids, float* x, void* xa, int width, int tokens, int f32, pk_stream st) {
+  if (!embed || !token_ids || !x || !xa || width <= 0 || tokens <= 0) return -1;
+  PK_BY_TYPE(f32, launch(embed_res32_kernel<float>, dim3(tokens), dim3(256), 0, st, true, (const float*)embed, token_ids, x, (float*)xa, width),
+             launch(embed_res32_kernel<bf16>, dim3(tokens), dim3(256), 0, st, true, (const bf16*)embed, token_ids, x, (bf16*)xa, width));
+  return (int)cudaGetLastError();
+}
+
+extern "C" int pk_res32_offset_norm_add(const void* y, int y_is_f32, const void* w, float* x, void* xa, int width, int tokens, float eps, int f32,
+                                        pk_stream st) {
+  if (!y || !w || !x || !xa || width <= 0 || tokens <= 0) return -1;
+  if (f32) {
+    launch(offset_norm_residual_kernel<float, float>, dim3(tokens), dim3(256), 0, st, true, (const float*)y, (const float*)w, x, (float*)xa, width, eps);
+  } else if (y_is_f32) {
+    launch(offset_norm_residual_kernel<bf16, float>, dim3(tokens), dim3(256), 0, st, true, (const float*)y, (const bf16*)w, x, (bf16*)xa, width, eps);
+  } else {
+    launch(offset_norm_residual_kernel<bf16, bf16>, dim3(tokens), dim3(256), 0, st, true, (const bf16*)y, (const bf16*)w, x, (bf16*)xa, width, eps);
+  }
+  return (int)cudaGetLastError();
+}
+
+extern "C" int pk_res32_offset_norm_rows(const float* x, const int* rows, const void* w, void* out, int width, int n_rows, float eps, int f32,
+                                         pk_stream st) {
+  if (!x || !rows || !w || !out || width <= 0 || n_rows <= 0) return -1;
+  PK_BY_TYPE(f32, launch(offset_norm_rows_kernel<float>, dim3(n_rows), dim3(256), 0, st, true, x, rows, (const float*)w, (float*)out, width, eps),
+             launch(offset_norm_rows_kernel<bf16>, dim3(n_rows), dim3(256), 0, st, true, x, rows, (const bf16*)w, (bf16*)out, width, eps));
+  return (int)cudaGetLastError();
+}
+
+extern "C" int pk_res32_skinny_proj(const void* W, const float* x, float* out, int M, int K, int tokens, int f32, pk_stream st) {
+  if (!W || !x || !out || M <= 0 || K <= 0 || tokens <= 0) return -1;
+  const int threads = M >= 8 ? 256 : 32 * M;
+  PK_BY_TYPE(f32, launch(skinny_proj_kernel<float>, dim3(tokens), dim3(threads), 0, st, true, (const float*)W, x, out, M, K),
+             launch(skinny_proj_kernel<bf16>, dim3(tokens), dim3(threads), 0, st, true, (const bf16*)W, x, out, M, K));
+  return (int)cudaGetLastError();
+}
+
+extern "C" int pk_act(const void* in, void* out, int F, int tokens, int kind, int f32, pk_stream st) {
+  if (!in || !out || F <= 0 || tokens <= 0 || kind < 0 || kind > 1) return -1;
+  const long total = (long)F * tokens;
+  PK_BY_TYPE(f32, launch(act_kernel<float>, dim3(grid_1d(total, 256)), dim3(256), 0, st, true, (const float*)in, (float*)out, F, total, kind),
+             launch(act_kernel<bf16>, dim3(grid_1d(total, 256)), dim3(256), 0, st, true, (const bf16*)in, (bf16*)out, F, total, kind));
+  return (int)cudaGetLastError();
+}
+
+extern "C" int pk_convert(const void* in, int in_f32, void* out, int out_f32, long n, pk_stream st) {
+  if (!in || !out || n <= 0) return -1;
+  const dim3 g(grid_1d(n, 256)), b(256);
+  if (in_f32 && out_f32) launch(convert_kernel<float, float>, g, b, 0, st, true, (const float*)in, (float*)out, n);
+  else if (in_f32) launch(convert_kernel<float, bf16>, g, b, 0, st, true, (const float*)in, (bf16*)out, n);
+  else if (out_f32) launch(convert_kernel<bf16, float>, g, b, 0, st, true, (const bf16*)in, (float*)out, n);
+  else launch(convert_kernel<bf16, bf16>, g, b, 0, st, true, (const bf16*)in, (bf16*)out, n);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int pk_gemm_strided(const void* A, const void* B, void* C, const float* row_scale, int rows, int cols, int K, long lda, long sbk,
+                               long sbn, long ldc, int batch, long bsA, long bsB, long bsC, int ld_scale, int scale_kind, int f32, pk_stream st) {
+  if (!A || !B || !C || rows <= 0 || cols <= 0 || K <= 0 || batch <= 0) return -1;
+  const dim3 g((cols + 63) / 64, (rows + 63) / 64, batch), b(256);
+  PK_BY_TYPE(f32,
+             launch(gemm_strided_kernel<float>, g, b, 0, st, true, (const float*)A, (const float*)B, (float*)C, row_scale, rows, cols, K, lda, sbk,
+                    sbn, ldc, bsA, bsB, bsC, ld_scale, scale_kind),
+             launch(gemm_strided_kernel<bf16>, g, b, 0, st, true, (const bf16*)A, (const bf16*)B, (bf16*)C, row_scale, rows, cols, K, lda, sbk, sbn,
+                    ldc, bsA, bsB, bsC, ld_scale, scale_kind));
+  return (int)cudaGetLastError();
+}

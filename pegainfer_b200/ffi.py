@@ -107,6 +107,25 @@ EXT_SIGNATURES = {
 }
 
 
+# fp32-residual / latent-attention / mixture-of-experts ops (element type chosen by an `f32` flag behind void pointers)
+i64l = C.c_long
+RES32_SIGNATURES = {
+    "pk_res32_embed": (i32, [vp, vp, vp, vp, i32, i32, i32, vp]),
+    "pk_res32_offset_norm_add": (i32, [vp, i32, vp, vp, vp, i32, i32, f32, i32, vp]),
+    "pk_res32_offset_norm_rows": (i32, [vp, vp, vp, vp, i32, i32, f32, i32, vp]),
+    "pk_res32_skinny_proj": (i32, [vp, vp, vp, i32, i32, i32, i32, vp]),
+    "pk_act": (i32, [vp, vp, i32, i32, i32, i32, vp]),
+    "pk_convert": (i32, [vp, i32, vp, i32, i64l, vp]),
+    "pk_gemm_strided": (i32, [vp, vp, vp, vp, i32, i32, i32, i64l, i64l, i64l, i64l, i32, i64l, i64l, i64l, i32, i32, i32, vp]),
+    "pk_rope_slice": (i32, [vp, vp, vp, vp, f32] + [i32] * 9 + [vp]),
+    "pk_latent_kv_append": (i32, [vp] * 7 + [i64l, i32, i32, i32, i32, vp, f32, f32, i32, i32, vp]),
+    "pk_latent_attention": (i32, [vp] * 8 + [i64l, i32, i32, i32, i32, i32, f32, i32, vp]),
+    "pk_router_grouped_topk": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, f32, vp]),
+    "pk_moe_up_relu2": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]),
+    "pk_moe_down_combine": (i32, [vp] * 7 + [i32, i32, i32, i32, i32, vp]),
+}
+
+
 def load(path: str | None = None, extensions: bool = True) -> C.CDLL:
     """dlopen a kernel library behind the pegainfer-kernels C ABI and type its symbols.
 
@@ -123,6 +142,7 @@ def load(path: str | None = None, extensions: bool = True) -> C.CDLL:
     if extensions:
         sigs.update(EXT_SIGNATURES)
         sigs.update(QWEN35_SIGNATURES)
+        sigs.update(RES32_SIGNATURES)
     for name, (res, args) in sigs.items():
         fn = getattr(lib, name)
         fn.restype = res
