@@ -440,10 +440,12 @@ int pk_latent_kv_append(const void* dkv, const void* norm_w, const int* position
                         void* cache, long page_stride, int page_size, int rank, int rot, int dims, const float* freq, float mag, float eps,
                         int tokens, int f32, pk_stream st);
 /* out[t,h,:rank] = sum_j softmax_j((qa[t,h] . [c_j | kr_j]) * scale; with exp(sink[h]) added to the denominator) c_j over the
- * request's cached positions j <= positions[t].  qa [tokens, heads, rank + rot] holds the query already folded onto the latent. */
+ * request's cached positions j <= positions[t].  qa [tokens, heads, rank + rot] holds the query already folded onto the latent.
+ * Tokens of one request are contiguous with ascending positions.  max_kv_len (0 = unknown) is the longest context in the batch: a
+ * hint for splitting the key axis when there are few query rows.  bf16 with rank % 64 == 0 and rot % 16 == 0 runs on the tensor cores. */
 int pk_latent_attention(const void* qa, const void* cache, const void* sink, const int* positions, const int* req, const int* page_off,
                         const int* pages, void* out, long page_stride, int page_size, int tokens, int heads, int rank, int rot, float scale,
-                        int f32, pk_stream st);
+                        int max_kv_len, int f32, pk_stream st);
 /* Group-limited top-k router over fp32 logits [tokens, experts]: ids / weights [tokens, top] (see moe.cu) */
 int pk_router_grouped_topk(const float* logits, int* ids, float* weights, int tokens, int experts, int top, int groups, int keep, float scale,
                            pk_stream st);

@@ -141,7 +141,7 @@ struct Model {
   bool finalize();
   bool ensure_scratch(int T, int R);
   bool lin(const Mat& W, const void* X, void* Y, int N);
-  bool run_layer(int li, int T, const int* d_pos, const int* d_req, const int* d_poff, const int* d_pages);
+  bool run_layer(int li, int T, int max_kv, const int* d_pos, const int* d_req, const int* d_poff, const int* d_pages);
   bool step(int n, const int* tokens, const int* lens, const int* rids, int n_rows, const int* rows, int want_sample);
 };
 
@@ -358,7 +358,7 @@ bool Model::lin(const Mat& W, const void* X, void* Y, int N) {
   return true;
 }
 
-bool Model::run_layer(int li, int T, const int* d_pos, const int* d_req, const int* d_poff, const int* d_pages) {
+bool Model::run_layer(int li, int T, int max_kv, const int* d_pos, const int* d_req, const int* d_poff, const int* d_pages) {
   Layer& L = layers[li];
   const LayerCfg& a = L.c;
   const int W = c.width, f32 = c.f32, H = a.heads, r = a.kv_rank, rd = a.rot_dim, D = r + rd;
@@ -382,7 +382,7 @@ bool Model::run_layer(int li, int T, const int* d_pos, const int* d_req, const i
     return false;
   if (!rc(k.pk_res32_skinny_proj(L.g.d.ptr, (const float*)x.ptr, (float*)gate.ptr, H, W, T, f32, st), "output gate")) return false;
   if (!rc(k.pk_latent_attention(qa.ptr, pool_base, L.sink.d.ptr, d_pos, d_req, d_poff, d_pages, olat.ptr, page_stride, c.page_size, T, H, r, rd,
-                                a.scale, f32, st),
+                                a.scale, max_kv, f32, st),
           "latent attention"))
     return false;
   // values: ao[:, h] = logistic(gate[:, h]) * (o_lat[:, h] W_uv[h]^T)
@@ -468,7 +468,7 @@ bool Model::step(int n, const int* tokens, const int* lens, const int* rids, int
   } txn{this, {}, false};
   // metadata block: [tok T][pos T][req T][page_off n][rows R][pages ...]
   std::vector<int> meta((size_t)3 * T + n + n_rows);
-  int t0 = 0;
+  int t0 = 0, max_kv = 0;
   std::vector<int> page_list;
   for (int i = 0; i < n; ++i) {
     pq::KvState& s = reqs[rids[i]];
@@ -483,6 +483,7 @@ bool Model::step(int n, const int* tokens, const int* lens, const int* rids, int
     meta[3 * T + i] = (int)page_list.size();
     page_list.insert(page_list.end(), s.pages.begin(), s.pages.end());
     s.seq_len += lens[i];
+    max_kv = std::max(max_kv, s.seq_len);
     t0 += lens[i];
   }
   for (int i = 0; i < n_rows; ++i) meta[3 * T + n + i] = rows[i];
@@ -503,7 +504,7 @@ bool Model::step(int n, const int* tokens, const int* lens, const int* rids, int
   const int *d_tok = M, *d_pos = M + T, *d_req = M + 2 * T, *d_poff = M + 3 * T, *d_rows = M + 3 * T + n, *d_pages = M + 3 * T + n + n_rows;
   if (!rc(k.pk_res32_embed(embed.d.ptr, d_tok, (float*)x.ptr, xa.ptr, c.width, T, c.f32, st), "embedding")) return false;
   for (int li = 0; li < c.n_layers; ++li)
-    if (!run_layer(li, T, d_pos, d_req, d_poff, d_pages)) return false;
+    if (!run_layer(li, T, max_kv, d_pos, d_req, d_poff, d_pages)) return false;
   if (n_rows > 0) {
     if (!rc(k.pk_res32_offset_norm_rows((const float*)x.ptr, d_rows, final_norm.d.ptr, xr.ptr, c.width, n_rows, c.eps, c.f32, st), "final norm"))
       return false;

@@ -11,6 +11,8 @@
 // the host builds the table, e.g. YaRN-blended), append of (normed latent, rotated key part) into the paged cache, and
 // the attention itself (generic widths, fp32 arithmetic; element type bf16 or float).
 // Cache layout: page p of owner layer l at base + p * page_stride + layer_off(l); inside, slot s at s * (rank + rot).
+#include <cstring>
+
 #include "common.cuh"
 #include "typed.cuh"
 
@@ -143,6 +145,19 @@ __global__ void latent_attention_kernel(const E* __restrict__ qa, const E* __res
   }
 }
 
+// latent_attention_mma.cu: tensor-core kernel for bf16 with rank % 64 == 0 and rot % 16 == 0; -2 = not for this shape
+int launch_latent_attention_mma(const bf16* qa, const bf16* cache, const bf16* sink, const int* pos, const int* req, const int* page_off,
+                                const int* pages, bf16* out, long page_stride, int page_size, int tokens, int heads, int rank, int rot, float scale,
+                                int max_kv_len, cudaStream_t st);
+static bool latent_mma_enabled() {  // PK_LATENT_ATTN=generic keeps the generic kernel for A/B runs
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("PK_LATENT_ATTN");
+    v = (e && strcmp(e, "generic") == 0) ? 0 : 1;
+  }
+  return v == 1;
+}
+
 }  // namespace pk
 
 using namespace pk;
@@ -176,8 +191,13 @@ extern "C" int pk_latent_kv_append(const void* dkv, const void* norm_w, const in
 
 extern "C" int pk_latent_attention(const void* qa, const void* cache, const void* sink, const int* positions, const int* req, const int* page_off,
                                    const int* pages, void* out, long page_stride, int page_size, int tokens, int heads, int rank, int rot,
-                                   float scale, int f32, pk_stream st) {
+                                   float scale, int max_kv_len, int f32, pk_stream st) {
   if (!qa || !cache || !sink || !positions || !req || !page_off || !pages || !out || tokens <= 0 || heads <= 0 || rank <= 0 || rot < 0) return -1;
+  if (!f32 && latent_mma_enabled()) {
+    const int rc = launch_latent_attention_mma((const bf16*)qa, (const bf16*)cache, (const bf16*)sink, positions, req, page_off, pages, (bf16*)out,
+                                               page_stride, page_size, tokens, heads, rank, rot, scale, max_kv_len, st);
+    if (rc != -2) return rc;
+  }
   if (rank > 32 * kLatentMaxPerLane) return -2;
   const int threads = 128, nw = threads / 32;
   const size_t smem = (size_t)(rank + rot + 2 * nw + nw * rank) * sizeof(float);

@@ -119,7 +119,7 @@ RES32_SIGNATURES = {
     "pk_gemm_strided": (i32, [vp, vp, vp, vp, i32, i32, i32, i64l, i64l, i64l, i64l, i32, i64l, i64l, i64l, i32, i32, i32, vp]),
     "pk_rope_slice": (i32, [vp, vp, vp, vp, f32] + [i32] * 9 + [vp]),
     "pk_latent_kv_append": (i32, [vp] * 7 + [i64l, i32, i32, i32, i32, vp, f32, f32, i32, i32, vp]),
-    "pk_latent_attention": (i32, [vp] * 8 + [i64l, i32, i32, i32, i32, i32, f32, i32, vp]),
+    "pk_latent_attention": (i32, [vp] * 8 + [i64l, i32, i32, i32, i32, i32, f32, i32, i32, vp]),
     "pk_router_grouped_topk": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, f32, vp]),
     "pk_moe_up_relu2": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]),
     "pk_moe_down_combine": (i32, [vp] * 7 + [i32, i32, i32, i32, i32, vp]),
