@@ -753,6 +753,105 @@ def tp_base_leg(cfg8, device):
         return {"available": False, "why": f"{type(e).__name__}: {e}"[:300]}
 
 
+# ------------------------------------------------------------------------------------ design comparison (--arch)
+def _arch_sizes():
+    """Layer shapes that resemble real models (random weights, few layers): a Vamadra stack and the Qwen3 stack of equal width,
+    head count, depth and vocabulary, with the feed-forward width of the experts a token activates."""
+    def vam(width, heads, dim, rot, vdim, rank, dense_ff, experts, top, groups, keep, eff, sff, vocab):
+        mx = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "kv_rank": rank, "scale": (dim + rot) ** -0.5,
+              "rot": {"dims": rot, "base": 10000.0, "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+        moe = {"kind": "moe", "expert": {"ff": eff}, "shared": {"ff": sff},
+               "router": {"experts": experts, "top": top, "scale": 1.0, "groups": {"count": groups, "keep": keep}}}
+        layers = [{"type": "latent_attention", "mixer": mx, "mlp": {"kind": "dense", "ff": dense_ff}},
+                  {"type": "latent_attention", "mixer": mx, "mlp": moe},
+                  {"type": "latent_attention", "mixer": dict(mx, kv_from=1), "mlp": moe},
+                  {"type": "latent_attention", "mixer": mx, "mlp": moe}]
+        return {"architecture": "Vamadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": layers}
+    from pegainfer_b200.config import Qwen3Config
+    return {
+        "w2048": (vam(2048, 16, 128, 64, 128, 512, 10944, 64, 6, 8, 4, 1408, 2816, 32768),
+                  Qwen3Config(2048, 6 * 1408 + 2816, 4, 16, 8, 128, 32768, 1e-6, 1e6, False, "qwen3-w2048")),
+        "w1024": (vam(1024, 8, 64, 32, 64, 256, 4096, 16, 2, 4, 2, 768, 1536, 32768),
+                  Qwen3Config(1024, 2 * 768 + 1536, 4, 8, 4, 128, 32768, 1e-6, 1e6, False, "qwen3-w1024")),
+    }
+
+
+def run_arch_compare(args):
+    """`--arch vamadra`: prefill and decode throughput of the Vamadra path beside the Qwen3 path at equal size.  Wall clock around
+    each public-API call (token ids from the host in, logits / token back out, stream synchronised), median of the repeats after
+    warm-up; between repeats nothing else runs on the GPU.  One JSON line."""
+    import torch
+    from pegainfer_b200.model import ModelRuntimeConfig, Qwen3Model
+    from pegainfer_b200.synthetic import iter_random_weights, synthetic_prompt
+    from pegainfer_b200.vamadra import VamadraConfig, VamadraModel, iter_random_weights as vam_weights
+    reps, warm = max(3, min(args.steps, 20)), max(3, min(args.warmup, 5))
+    prompts, ctx, dec_steps = [512, 2048], 2048, 32
+    out = {"metric": "prefill_and_decode_tok_s", "arch": "vamadra", "beside": "qwen3", "dtype": "bf16", "data": "synthetic", "n_gpus": 1,
+           "timing": "wall clock around the public API call incl. host->device ids and device->host result, stream synchronised", "sizes": {}}
+
+    def med(f):
+        for _ in range(warm):
+            f()
+        ts = []
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            f()
+            ts.append(time.perf_counter() - t0)
+        return statistics.median(ts)
+
+    for name, (vcfg_d, qcfg) in _arch_sizes().items():
+        if args.arch_size and name not in args.arch_size.split(","):
+            continue
+        row = {}
+        vcfg = VamadraConfig.from_dict(vcfg_d)
+        vm = VamadraModel(vcfg, vam_weights(vcfg, 0, "cuda"), max_tokens=4 * (ctx + 64) + max(prompts), max_requests=5)
+        res = {}
+        for T in prompts:
+            toks = synthetic_prompt(T)
+
+            def pre():
+                rid = vm.alloc_request()
+                vm.step([(rid, toks)])
+                vm.drop_request(rid)
+            res[f"prefill_{T}_tok_s"] = round(T / med(pre), 1)
+        for bs in (1, 4):
+            rids = [vm.alloc_request() for _ in range(bs)]
+            vm.step([(r, synthetic_prompt(ctx, i)) for i, r in enumerate(rids)])
+            vm.launch_count(True)
+            t = med(lambda: vm.step([(r, [7]) for r in rids], sample=True))
+            res[f"decode_bs{bs}_ctx{ctx}_tok_s"] = round(bs / t, 1)
+            res[f"decode_bs{bs}_launches_per_step"] = vm.launch_count() // (warm + reps)
+            for r in rids:
+                vm.drop_request(r)
+        row["vamadra"] = res
+        vm.close()
+        qm = Qwen3Model(qcfg, iter_random_weights(qcfg, seed=0, device="cuda"),
+                        ModelRuntimeConfig(enable_cuda_graph=True, fused=True, num_pages=(4 * (ctx + 64) + max(prompts)) // 16 + 8, max_batch=4))
+        res = {}
+        for T in prompts:
+            toks = synthetic_prompt(T)
+
+            def pre_q():
+                kid = qm.alloc_kv()
+                qm.prefill([toks], [kid])
+                qm.drop_request(kid)
+            res[f"prefill_{T}_tok_s"] = round(T / med(pre_q), 1)
+        for bs in (1, 4):
+            kids = [qm.alloc_kv() for _ in range(bs)]
+            for i, kdx in enumerate(kids):
+                qm.prefill([synthetic_prompt(ctx, i)], [kdx])
+            t = med(lambda: qm.decode([7] * bs, kids, want_logits=False))
+            res[f"decode_bs{bs}_ctx{ctx}_tok_s"] = round(bs / t, 1)
+            for kdx in kids:
+                qm.drop_request(kdx)
+        res["decode_launches_per_step"] = qm.launches_per_step()
+        row["qwen3"] = res
+        qm.close()
+        out["sizes"][name] = row
+    out["config"] = {"prompts": prompts, "decode_ctx": ctx, "repeats": reps, "warmup": warm, "layers": 4}
+    print(json.dumps(out), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -768,7 +867,13 @@ def main():
     ap.add_argument("--weights", default="cpu", choices=["cpu", "cuda"],
                     help="cpu (default): the seed-0 CPU checkpoint the oracle fixtures were computed on; cuda: generated on "
                          "each GPU (fast; tuning sweeps only -- the parity key then reports a different checkpoint)")
+    ap.add_argument("--arch", default=None, choices=["vamadra"],
+                    help="instead of the headline workload: prefill / decode throughput of this design beside Qwen3 at equal size")
+    ap.add_argument("--arch-size", default=None, help="with --arch: comma-separated subset of the sizes (w2048,w1024)")
     args = ap.parse_args()
+    if args.arch:
+        run_arch_compare(args)
+        return
     if args.quick:
         args.no_cpu_baseline = args.no_gpu_reference = args.no_tp_base = args.no_config4 = True
     if args.warmup < 3:

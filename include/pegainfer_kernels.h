@@ -454,6 +454,11 @@ int pk_moe_up_relu2(const void* xa, const void* w_up, const int* ids, void* hid,
 /* y[t] = sum_k weights[t,k] W_down[ids[t,k]] hid[t,k,:] (+ logistic(shared_gate[t]) * shared[t] when shared != NULL); y fp32 */
 int pk_moe_down_combine(const void* hid, const void* w_down, const int* ids, const float* weights, const void* shared,
                         const float* shared_gate, float* y, int tokens, int top, int width, int ff, int f32, pk_stream st);
+/* The same feed-forward for many tokens (bf16): pairs bucketed by expert, one tensor-core GEMM per expert's rows (moe_grouped.cu).
+ * workspace: pk_moe_grouped_workspace_bytes() bytes, 256-byte aligned.  -2: width or ff not a multiple of 8, or misaligned. */
+long pk_moe_grouped_workspace_bytes(int tokens, int top, int experts, int width, int ff);
+int pk_moe_grouped_relu2(const void* xa, const void* w_up, const void* w_down, const int* ids, const float* weights, const void* shared,
+                         const float* shared_gate, float* y, void* workspace, int tokens, int top, int experts, int width, int ff, pk_stream st);
 
 #ifdef __cplusplus
 }

@@ -52,6 +52,7 @@ struct Lib {
   PV_FN(pk_b200_launch_count) PV_FN(pk_res32_embed) PV_FN(pk_res32_offset_norm_add) PV_FN(pk_res32_offset_norm_rows)
   PV_FN(pk_res32_skinny_proj) PV_FN(pk_act) PV_FN(pk_convert) PV_FN(pk_gemm_strided) PV_FN(pk_rope_slice) PV_FN(pk_latent_kv_append)
   PV_FN(pk_latent_attention) PV_FN(pk_router_grouped_topk) PV_FN(pk_moe_up_relu2) PV_FN(pk_moe_down_combine)
+  PV_FN(pk_moe_grouped_workspace_bytes) PV_FN(pk_moe_grouped_relu2)
 #undef PV_FN
   std::string load(const std::string& p) {
     handle = dlopen(p.c_str(), RTLD_NOW | RTLD_LOCAL);
@@ -64,6 +65,7 @@ struct Lib {
     PV_REQ(pk_b200_launch_count) PV_REQ(pk_res32_embed) PV_REQ(pk_res32_offset_norm_add) PV_REQ(pk_res32_offset_norm_rows)
     PV_REQ(pk_res32_skinny_proj) PV_REQ(pk_act) PV_REQ(pk_convert) PV_REQ(pk_gemm_strided) PV_REQ(pk_rope_slice) PV_REQ(pk_latent_kv_append)
     PV_REQ(pk_latent_attention) PV_REQ(pk_router_grouped_topk) PV_REQ(pk_moe_up_relu2) PV_REQ(pk_moe_down_combine)
+    PV_REQ(pk_moe_grouped_workspace_bytes) PV_REQ(pk_moe_grouped_relu2)
 #undef PV_REQ
     return missing.empty() ? "" : "kernel library " + p + " lacks:" + missing;
   }
@@ -71,6 +73,8 @@ struct Lib {
     if (handle) dlclose(handle);
   }
 };
+
+static const int kGroupedMinTokens = 32;  // from this many tokens in a step the experts run bucketed
 
 struct Mat {
   DeviceBuf d;
@@ -104,7 +108,7 @@ struct Model {
   // per-step scratch, grown to the largest step seen
   int cap_t = 0, cap_r = 0;
   DeviceBuf x, xa, q, dkv, qa, gate, olat, ao, mix, gu, act, z, ids, wts, hid, yf, sgl, sh, xr, logits_e, logits_f, logits_bf, sampled_d, top1_val,
-      top1_states, trail;
+      top1_states, trail, moe_ws;
   DeviceBuf meta_d;
   int* meta_h = nullptr;
   size_t meta_cap = 0;
@@ -338,6 +342,12 @@ bool Model::ensure_scratch(int T, int R) {
          act.alloc_uninit(n * std::max(mx_act, 1) * es) && z.alloc_uninit(n * std::max(mx_e, 1) * 4) && ids.alloc_uninit(n * std::max(mx_top, 1) * 4) &&
          wts.alloc_uninit(n * std::max(mx_top, 1) * 4) && hid.alloc_uninit(n * std::max(mx_hid, 1) * es) && yf.alloc_uninit(n * W * 4) &&
          sgl.alloc_uninit(n * 4) && sh.alloc_uninit(n * W * es);
+    if (ok && !c.f32 && (int)n >= kGroupedMinTokens) {  // bucketed experts for prompt portions
+      long ws = 0;
+      for (auto& L : layers)
+        if (L.c.mlp_kind == 2) ws = std::max(ws, k.pk_moe_grouped_workspace_bytes((int)n, L.c.top, L.c.experts, c.width, L.c.expert_ff));
+      ok = ws == 0 || moe_ws.alloc_uninit((size_t)ws);
+    }
     if (ok) cap_t = (int)n;
   }
   if (ok && R > cap_r) {
@@ -403,7 +413,6 @@ bool Model::run_layer(int li, int T, int max_kv, const int* d_pos, const int* d_
     if (!rc(k.pk_router_grouped_topk((const float*)z.ptr, (int*)ids.ptr, (float*)wts.ptr, T, a.experts, a.top, a.groups, a.keep, a.route_scale, st),
             "router top-k"))
       return false;
-    if (!rc(k.pk_moe_up_relu2(xa.ptr, L.e_up.d.ptr, (const int*)ids.ptr, hid.ptr, T, a.top, W, a.expert_ff, f32, st), "experts up")) return false;
     const void* shared = nullptr;
     if (a.shared_ff > 0) {
       if (!lin(L.s_up, xa.ptr, gu.ptr, T)) return false;
@@ -412,7 +421,17 @@ bool Model::run_layer(int li, int T, int max_kv, const int* d_pos, const int* d_
       if (!rc(k.pk_res32_skinny_proj(L.s_gate.d.ptr, (const float*)x.ptr, (float*)sgl.ptr, 1, W, T, f32, st), "shared expert gate")) return false;
       shared = sh.ptr;
     }
-    if (!rc(k.pk_moe_down_combine(hid.ptr, L.e_down.d.ptr, (const int*)ids.ptr, (const float*)wts.ptr, shared, (const float*)sgl.ptr, (float*)yf.ptr, T,
+    // many tokens: rows bucketed by expert on the tensor cores; a few tokens: per token, reading only the chosen experts' weights
+    int grouped = -2;
+    if (!f32 && T >= kGroupedMinTokens && moe_ws.ptr) {
+      grouped = k.pk_moe_grouped_relu2(xa.ptr, L.e_up.d.ptr, L.e_down.d.ptr, (const int*)ids.ptr, (const float*)wts.ptr, shared, (const float*)sgl.ptr,
+                                       (float*)yf.ptr, moe_ws.ptr, T, a.top, a.experts, W, a.expert_ff, st);
+      if (grouped != -2 && !rc(grouped, "experts (grouped)")) return false;
+    }
+    if (grouped == -2 && !rc(k.pk_moe_up_relu2(xa.ptr, L.e_up.d.ptr, (const int*)ids.ptr, hid.ptr, T, a.top, W, a.expert_ff, f32, st), "experts up"))
+      return false;
+    if (grouped == -2 &&
+        !rc(k.pk_moe_down_combine(hid.ptr, L.e_down.d.ptr, (const int*)ids.ptr, (const float*)wts.ptr, shared, (const float*)sgl.ptr, (float*)yf.ptr, T,
                                   a.top, W, a.expert_ff, f32, st),
             "experts down"))
       return false;

@@ -92,7 +92,9 @@ __global__ void router_grouped_topk_kernel(const float* __restrict__ z, int* __r
   if (lane < top) wts[(size_t)t * top + lane] = wts[(size_t)t * top + lane] / (total + 1e-20f) * scale;
 }
 
-// hid[t, k, f] = act(W_up[ids[t,k]][f] . x[t]); act = relu^2.  One block per (token, choice).
+constexpr int kMoeRowsPerBlock = 32;  // weight rows per CTA: a decode step spreads one expert over many SMs
+
+// hid[t, k, f] = act(W_up[ids[t,k]][f] . x[t]); act = relu^2.  Grid (token, choice, slice of ff rows).
 template <typename E>
 __global__ void moe_up_kernel(const E* __restrict__ xa, const E* __restrict__ w_up, const int* __restrict__ ids, E* __restrict__ hid, int width,
                               int ff) {
@@ -103,7 +105,8 @@ __global__ void moe_up_kernel(const E* __restrict__ xa, const E* __restrict__ w_
   for (int i = threadIdx.x; i < width; i += blockDim.x) xs[i] = to_f(xa[(size_t)tok * width + i]);
   __syncthreads();
   const E* W = w_up + (size_t)ids[(size_t)tok * top + k] * ff * width;
-  for (int f = warp; f < ff; f += nw) {
+  const int f_end = min(ff, (int)(blockIdx.z + 1) * kMoeRowsPerBlock);
+  for (int f = blockIdx.z * kMoeRowsPerBlock + warp; f < f_end; f += nw) {
     const E* wr = W + (size_t)f * width;
     float acc = 0.f;
     for (int i = lane; i < width; i += 32) acc = fmaf(to_f(wr[i]), xs[i], acc);
@@ -115,7 +118,7 @@ __global__ void moe_up_kernel(const E* __restrict__ xa, const E* __restrict__ w_
   }
 }
 
-// y[t][i] = sum_k wts[t,k] * (W_down[ids[t,k]][i] . hid[t,k]) + logistic(sg[t]) * shared[t][i]; fp32 out.  One block per token.
+// y[t][i] = sum_k wts[t,k] * (W_down[ids[t,k]][i] . hid[t,k]) + logistic(sg[t]) * shared[t][i]; fp32 out.  Grid (token, slice of output rows).
 template <typename E>
 __global__ void moe_down_kernel(const E* __restrict__ hid, const E* __restrict__ w_down, const int* __restrict__ ids, const float* __restrict__ wts,
                                 const E* __restrict__ shared, const float* __restrict__ sg, float* __restrict__ y, int width, int ff, int top) {
@@ -125,7 +128,8 @@ __global__ void moe_down_kernel(const E* __restrict__ hid, const E* __restrict__
   for (int i = threadIdx.x; i < top * ff; i += blockDim.x) hs[i] = to_f(hid[(size_t)t * top * ff + i]);
   __syncthreads();
   const float g = shared ? 1.f / (1.f + expf(-sg[t])) : 0.f;
-  for (int i = warp; i < width; i += nw) {
+  const int i_end = min(width, (int)(blockIdx.y + 1) * kMoeRowsPerBlock);
+  for (int i = blockIdx.y * kMoeRowsPerBlock + warp; i < i_end; i += nw) {
     float tot = 0.f;
     for (int k = 0; k < top; ++k) {
       const E* wr = w_down + ((size_t)ids[(size_t)t * top + k] * width + i) * ff;
@@ -156,9 +160,9 @@ extern "C" int pk_moe_up_relu2(const void* xa, const void* w_up, const int* ids,
   if (!xa || !w_up || !ids || !hid || tokens <= 0 || top <= 0 || width <= 0 || ff <= 0) return -1;
   const size_t smem = (size_t)width * sizeof(float);
   if (f32)
-    launch(moe_up_kernel<float>, dim3(tokens, top), dim3(256), smem, st, true, (const float*)xa, (const float*)w_up, ids, (float*)hid, width, ff);
+    launch(moe_up_kernel<float>, dim3(tokens, top, (ff + kMoeRowsPerBlock - 1) / kMoeRowsPerBlock), dim3(256), smem, st, true, (const float*)xa, (const float*)w_up, ids, (float*)hid, width, ff);
   else
-    launch(moe_up_kernel<bf16>, dim3(tokens, top), dim3(256), smem, st, true, (const bf16*)xa, (const bf16*)w_up, ids, (bf16*)hid, width, ff);
+    launch(moe_up_kernel<bf16>, dim3(tokens, top, (ff + kMoeRowsPerBlock - 1) / kMoeRowsPerBlock), dim3(256), smem, st, true, (const bf16*)xa, (const bf16*)w_up, ids, (bf16*)hid, width, ff);
   return (int)cudaGetLastError();
 }
 
@@ -169,11 +173,11 @@ extern "C" int pk_moe_down_combine(const void* hid, const void* w_down, const in
   if (smem > 200 * 1024) return -2;
   if (f32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_down_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    launch(moe_down_kernel<float>, dim3(tokens), dim3(256), smem, st, true, (const float*)hid, (const float*)w_down, ids, weights,
+    launch(moe_down_kernel<float>, dim3(tokens, (width + kMoeRowsPerBlock - 1) / kMoeRowsPerBlock), dim3(256), smem, st, true, (const float*)hid, (const float*)w_down, ids, weights,
            (const float*)shared, shared_gate, y, width, ff, top);
   } else {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_down_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    launch(moe_down_kernel<bf16>, dim3(tokens), dim3(256), smem, st, true, (const bf16*)hid, (const bf16*)w_down, ids, weights, (const bf16*)shared,
+    launch(moe_down_kernel<bf16>, dim3(tokens, (width + kMoeRowsPerBlock - 1) / kMoeRowsPerBlock), dim3(256), smem, st, true, (const bf16*)hid, (const bf16*)w_down, ids, weights, (const bf16*)shared,
            shared_gate, y, width, ff, top);
   }
   return (int)cudaGetLastError();

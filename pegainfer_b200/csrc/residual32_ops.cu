@@ -66,7 +66,7 @@ __global__ void skinny_proj_kernel(const E* __restrict__ W, const float* __restr
   pdl_wait();
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const float* xr = x + (size_t)t * K;
-  for (int m = warp; m < M; m += nw) {
+  for (int m = blockIdx.y * nw + warp; m < M; m += gridDim.y * nw) {
     const E* wr = W + (size_t)m * K;
     float acc = 0.f;
     for (int k = lane; k < K; k += 32) acc = fmaf(to_f(wr[k]), xr[k], acc);
@@ -213,9 +213,10 @@ extern "C" int pk_res32_offset_norm_rows(const float* x, const int* rows, const 
 
 extern "C" int pk_res32_skinny_proj(const void* W, const float* x, float* out, int M, int K, int tokens, int f32, pk_stream st) {
   if (!W || !x || !out || M <= 0 || K <= 0 || tokens <= 0) return -1;
-  const int threads = M >= 8 ? 256 : 32 * M;
-  PK_BY_TYPE(f32, launch(skinny_proj_kernel<float>, dim3(tokens), dim3(threads), 0, st, true, (const float*)W, x, out, M, K),
-             launch(skinny_proj_kernel<bf16>, dim3(tokens), dim3(threads), 0, st, true, (const bf16*)W, x, out, M, K));
+  const int threads = M >= 4 ? 128 : 32 * M;
+  const dim3 grid(tokens, tokens >= 256 ? 1 : (M + 3) / 4);  // few tokens: spread the rows over CTAs
+  PK_BY_TYPE(f32, launch(skinny_proj_kernel<float>, grid, dim3(threads), 0, st, true, (const float*)W, x, out, M, K),
+             launch(skinny_proj_kernel<bf16>, grid, dim3(threads), 0, st, true, (const bf16*)W, x, out, M, K));
   return (int)cudaGetLastError();
 }
 

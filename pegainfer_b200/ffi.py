@@ -123,6 +123,8 @@ RES32_SIGNATURES = {
     "pk_router_grouped_topk": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, f32, vp]),
     "pk_moe_up_relu2": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]),
     "pk_moe_down_combine": (i32, [vp] * 7 + [i32, i32, i32, i32, i32, vp]),
+    "pk_moe_grouped_workspace_bytes": (i64l, [i32, i32, i32, i32, i32]),
+    "pk_moe_grouped_relu2": (i32, [vp] * 9 + [i32, i32, i32, i32, i32, vp]),
 }
 
 

@@ -404,6 +404,42 @@ def test_moe_feed_forward(lib, dtype, shared):
     assert torch.allclose(y.cpu(), want, atol=tol, rtol=tol)
 
 
+@pytest.mark.parametrize("T,W,E,top,ff,shared", [(70, 40, 6, 2, 24, 16), (200, 72, 5, 3, 40, 0), (33, 64, 9, 1, 64, 8)])
+def test_moe_grouped_by_expert_matches_the_per_token_form(lib, T, W, E, top, ff, shared):
+    """prompt-sized batches bucket the (token, choice) pairs by expert and run one tensor-core product per expert (bf16): experts
+    with no rows, with a few and with more than one 64-row tile all occur"""
+    P = Hold()
+    g = torch.Generator().manual_seed(T)
+    r = lambda *s: (torch.randn(*s, generator=g) / math.sqrt(s[-1])).to(BF16).to(F32)
+    x = torch.randn(T, W, generator=g).to(BF16).to(F32)
+    z = 3.0 * torch.randn(T, E, generator=g)
+    z[:, 0] += 2.0       # a crowded expert
+    z[:, E - 1] -= 30.0  # and one that nobody picks
+    w = {f"e{e}.up": r(ff, W) for e in range(E)}
+    w.update({f"e{e}.down": r(W, ff) for e in range(E)})
+    ids_o, wts_o = O.grouped_top_router(z, top, 1, 1, 1.0)
+    want = torch.zeros(T, W)
+    for t in range(T):
+        for e, gw in zip(ids_o[t].tolist(), wts_o[t]):
+            want[t] += gw * O.relu2_expert(x[t:t + 1], w[f"e{e}.up"], w[f"e{e}.down"])[0]
+    sh_ptr = sg_ptr = None
+    if shared:
+        su, sd, sg = r(shared, W), r(W, shared), torch.randn(T, generator=g)
+        sh = O.relu2_expert(x, su, sd).to(BF16).to(F32)
+        want = want + sh * torch.sigmoid(sg)[:, None]
+        sh_ptr, sg_ptr = P(dev(sh, BF16)), P(sg.cuda())
+    ids = ids_o.to(torch.int32).cuda().contiguous()
+    wts = wts_o.cuda().contiguous()
+    up = dev(torch.cat([w[f"e{e}.up"] for e in range(E)]), BF16)
+    down = dev(torch.cat([w[f"e{e}.down"] for e in range(E)]), BF16)
+    ws = torch.zeros(lib.pk_moe_grouped_workspace_bytes(T, top, E, W, ff), dtype=torch.uint8, device="cuda")
+    y = torch.zeros(T, W, device="cuda")
+    assert lib.pk_moe_grouped_relu2(P(dev(x, BF16)), up.data_ptr(), down.data_ptr(), ids.data_ptr(), wts.data_ptr(), sh_ptr, sg_ptr, y.data_ptr(),
+                                    ws.data_ptr(), T, top, E, W, ff, None) == 0
+    torch.cuda.synchronize()
+    assert torch.allclose(y.cpu(), want, atol=3e-2, rtol=3e-2)
+
+
 @pytest.mark.parametrize("dtype", [F32, BF16])
 def test_offset_norm_residual_and_rows(lib, dtype):
     P = Hold()
