@@ -82,7 +82,7 @@ struct Mat {
 };
 struct Layer {
   LayerCfg c{};
-  Mat norm1, norm2, q, dkv, dkv_norm, uk, uv, sink, g, o;  // mixer
+  Mat norm1, norm2, q, dkv, dkv_norm, uk, uk_t, uv, sink, g, o;  // mixer; uk_t = W_uk per head as [rank, dim] (made at load)
   Mat gate_up, down;                                       // dense: [gate ; up] stacked
   Mat e_up, e_down, router, s_up, s_down, s_gate;          // experts stacked [experts * ff, width] / [experts * width, ff]
   DeviceBuf freq;                                          // [rot_dims / 2] fp32 angular frequencies
@@ -239,7 +239,19 @@ bool Model::load_tensor(const std::string& name, const void* data, int rows, int
   else if (sub == "mix.q") ok = put(L.q, a.heads * (a.dim + a.rot_dim), W, 0, data, a.heads * (a.dim + a.rot_dim), name, rows, cols);
   else if (sub == "mix.dkv" && a.kv_from < 0) ok = put(L.dkv, a.kv_rank + a.rot_dim, W, 0, data, a.kv_rank + a.rot_dim, name, rows, cols);
   else if (sub == "mix.dkv.norm" && a.kv_from < 0) ok = put(L.dkv_norm, 1, a.kv_rank, 0, data, 1, name, rows, cols);
-  else if (sub == "mix.uk") ok = put(L.uk, a.heads * a.dim, a.kv_rank, 0, data, a.heads * a.dim, name, rows, cols);
+  else if (sub == "mix.uk") {
+    ok = put(L.uk, a.heads * a.dim, a.kv_rank, 0, data, a.heads * a.dim, name, rows, cols);
+    if (ok) {  // the query fold contracts over `dim`: keep a copy with that axis contiguous, [head][rank][dim]
+      const size_t n = (size_t)a.heads * a.dim * a.kv_rank;
+      std::vector<char> src(n * es), dst(n * es);
+      ok = cu(cudaMemcpy(src.data(), data, n * es, cudaMemcpyDefault), name.c_str());
+      for (int h = 0; h < a.heads && ok; ++h)
+        for (int d = 0; d < a.dim; ++d)
+          for (int r = 0; r < a.kv_rank; ++r)
+            memcpy(&dst[(((size_t)h * a.kv_rank + r) * a.dim + d) * es], &src[(((size_t)h * a.dim + d) * a.kv_rank + r) * es], es);
+      ok = ok && put(L.uk_t, a.heads * a.kv_rank, a.dim, 0, dst.data(), a.heads * a.kv_rank, name, a.heads * a.kv_rank, a.dim);
+    }
+  }
   else if (sub == "mix.uv") ok = put(L.uv, a.heads * a.vdim, a.kv_rank, 0, data, a.heads * a.vdim, name, rows, cols);
   else if (sub == "mix.sink") ok = put(L.sink, 1, a.heads, 0, data, 1, name, rows, cols);
   else if (sub == "mix.g") ok = put(L.g, a.heads, W, 0, data, a.heads, name, rows, cols);
@@ -383,8 +395,8 @@ bool Model::run_layer(int li, int T, int max_kv, const int* d_pos, const int* d_
       return false;
   }
   // fold the unrotated query onto the latent (per head: qa[:, :r] = q_unrotated W_uk[h]), rotate the other part beside it
-  if (!rc(k.pk_gemm_strided(q.ptr, L.uk.d.ptr, qa.ptr, nullptr, T, r, a.dim, (long)H * (a.dim + rd), r, 1, (long)H * D, H, a.dim + rd, (long)a.dim * r,
-                            D, 0, 0, f32, st),
+  if (!rc(k.pk_gemm_strided(q.ptr, L.uk_t.d.ptr, qa.ptr, nullptr, T, r, a.dim, (long)H * (a.dim + rd), 1, a.dim, (long)H * D, H, a.dim + rd,
+                            (long)a.dim * r, D, 0, 0, f32, st),
           "query fold"))
     return false;
   if (rd > 0 && !rc(k.pk_rope_slice(q.ptr, qa.ptr, d_pos, (const float*)L.freq.ptr, L.mag, T, H, a.dim + rd, a.dim, D, r, rd, a.rot_dims, f32, st),

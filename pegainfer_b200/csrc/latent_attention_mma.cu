@@ -15,31 +15,33 @@
 
 namespace pk {
 
-constexpr int kMmaRows = 16, kMmaKeys = 64, kMmaThreads = 128;
+constexpr int kMmaKeys = 64, kMmaThreads = 128;
 constexpr float kNegBig = -1e30f;
 
-// NV = 8-column output tiles per warp (rank = 32 * nv with nv <= NV, nv even)
-template <int NV>
+// NV = 8-column output tiles per warp (rank = 32 * nv with nv <= NV, nv even); MT = 16-row query tiles per CTA (2 for prompt
+// portions: every fetched key tile and every K / V fragment then serves 32 rows; 1 for the few rows of a decode step)
+template <int NV, int MT>
 __global__ void __launch_bounds__(kMmaThreads)
 latent_attention_mma_kernel(const bf16* __restrict__ qa, const bf16* __restrict__ cache, const bf16* __restrict__ sink, const int* __restrict__ pos,
                             const int* __restrict__ req, const int* __restrict__ page_off, const int* __restrict__ pages, bf16* __restrict__ out,
                             float* __restrict__ part_o, float* __restrict__ part_ml, long page_stride, int page_size, int tokens, int heads, int rank,
                             int rot, float scale) {
+  constexpr int ROWS = 16 * MT, NR = 2 * MT;  // NR = rows per thread: g + 8 * i, i < NR
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int D = rank + rot, ldk = D + 8, nv = rank / 32;
-  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);   // [16][ldk]
-  bf16* Ks = Qs + kMmaRows * ldk;                 // [2][64][ldk]
-  bf16* Ps = Ks + 2 * kMmaKeys * ldk;             // [16][72]
-  float* wmax = reinterpret_cast<float*>(Ps + kMmaRows * 72);  // [4][16]
-  float* wsum = wmax + 64;                                     // [4][16]
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);   // [ROWS][ldk]
+  bf16* Ks = Qs + ROWS * ldk;                     // [2][64][ldk]
+  bf16* Ps = Ks + 2 * kMmaKeys * ldk;             // [ROWS][72]
+  float* wmax = reinterpret_cast<float*>(Ps + ROWS * 72);  // [4][ROWS]
+  float* wsum = wmax + 4 * ROWS;                           // [4][ROWS]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tq = lane & 3;
-  const int total_rows = tokens * heads, R0 = blockIdx.x * kMmaRows;
+  const int total_rows = tokens * heads, R0 = blockIdx.x * ROWS;
   const int split = blockIdx.y, nsplit = gridDim.y;
   pdl_wait();
 
   // ---- Q tile (rows past the end are zero)
   const int chunks = D / 8;  // 16-byte pieces per row
-  for (int e = tid; e < kMmaRows * chunks; e += kMmaThreads) {
+  for (int e = tid; e < ROWS * chunks; e += kMmaThreads) {
     const int r = e / chunks, c = e % chunks;
     bf16* dst = Qs + r * ldk + c * 8;
     if (R0 + r < total_rows) cp_async16(dst, qa + (size_t)(R0 + r) * D + c * 8);
@@ -47,20 +49,26 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, const bf16* __restrict_
   }
   cp_async_commit();
 
-  // the two rows this thread owns in every accumulator: g and g + 8
-  int row_tok[2], row_pos[2];
+  int row_tok[NR], row_pos[NR];
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
+  for (int i = 0; i < NR; ++i) {
     const int R = R0 + g + 8 * i;
     row_tok[i] = R < total_rows ? R / heads : -1;
     row_pos[i] = row_tok[i] >= 0 ? pos[row_tok[i]] : -1;
   }
-  float m_run[2] = {kNegBig, kNegBig}, l_run[2] = {0.f, 0.f};
-  float o[NV][4];
+  float m_run[NR], l_run[NR];
 #pragma unroll
-  for (int i = 0; i < NV; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  for (int i = 0; i < NR; ++i) {
+    m_run[i] = kNegBig;
+    l_run[i] = 0.f;
+  }
+  float o[MT][NV][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int i = 0; i < NV; ++i) o[mt][i][0] = o[mt][i][1] = o[mt][i][2] = o[mt][i][3] = 0.f;
 
-  const int t_first = R0 / heads, t_last = (min(total_rows, R0 + kMmaRows) - 1) / heads;
+  const int t_first = R0 / heads, t_last = (min(total_rows, R0 + ROWS) - 1) / heads;
   int t = t_first;
   while (t <= t_last) {
     const int rq = req[t];
@@ -70,9 +78,9 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, const bf16* __restrict_
     const int per = ((kv_end + nsplit - 1) / nsplit + kMmaKeys - 1) / kMmaKeys * kMmaKeys;
     const int k_begin = split * per, k_end = min(kv_end, k_begin + per);
     const int* pg = pages + page_off[rq];
-    bool act[2];
+    bool act[NR];
 #pragma unroll
-    for (int i = 0; i < 2; ++i) act[i] = row_tok[i] >= t && row_tok[i] <= t_end;
+    for (int i = 0; i < NR; ++i) act[i] = row_tok[i] >= t && row_tok[i] <= t_end;
 
     auto load_keys = [&](int j0, int buf) {
       bf16* base = Ks + (size_t)buf * kMmaKeys * ldk;
@@ -94,85 +102,107 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, const bf16* __restrict_
       if (j0 + kMmaKeys < k_end) load_keys(j0 + kMmaKeys, buf ^ 1);
       const bf16* Kt = Ks + (size_t)buf * kMmaKeys * ldk;
 
-      // ---- S = Q K^T for this warp's 16 keys
-      float s[2][4] = {};
+      // ---- S = Q K^T for this warp's 16 keys, all query tiles
+      float s[MT][2][4];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) s[mt][nt][0] = s[mt][nt][1] = s[mt][nt][2] = s[mt][nt][3] = 0.f;
       for (int kk = 0; kk < D; kk += 16) {
-        uint32_t a[4], b[4];
-        ldsm_x4(a, Qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * ldk + kk + ((lane >> 4) & 1) * 8);
+        uint32_t b[4];
         ldsm_x4(b, Kt + (warp * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * ldk + kk + ((lane >> 3) & 1) * 8);
-        mma_bf16_16816(s[0], a, b[0], b[1]);
-        mma_bf16_16816(s[1], a, b[2], b[3]);
-      }
-      float mx[2] = {kNegBig, kNegBig};
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int i = e >> 1, j = j0 + warp * 16 + nt * 8 + 2 * tq + (e & 1);
-          const bool vis = act[i] && j < k_end && j <= row_pos[i];
-          s[nt][e] = vis ? s[nt][e] * scale : kNegBig;
-          mx[i] = fmaxf(mx[i], s[nt][e]);
+        for (int mt = 0; mt < MT; ++mt) {
+          uint32_t a[4];
+          ldsm_x4(a, Qs + (mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldk + kk + ((lane >> 4) & 1) * 8);
+          mma_bf16_16816(s[mt][0], a, b[0], b[1]);
+          mma_bf16_16816(s[mt][1], a, b[2], b[3]);
         }
+      }
+      float mx[NR];
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
+      for (int i = 0; i < NR; ++i) mx[i] = kNegBig;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i = mt * 2 + (e >> 1), j = j0 + warp * 16 + nt * 8 + 2 * tq + (e & 1);
+            const bool vis = act[i] && j < k_end && j <= row_pos[i];
+            s[mt][nt][e] = vis ? s[mt][nt][e] * scale : kNegBig;
+            mx[i] = fmaxf(mx[i], s[mt][nt][e]);
+          }
+#pragma unroll
+      for (int i = 0; i < NR; ++i) {
         mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
         mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
-        if (tq == 0) wmax[warp * 16 + g + 8 * i] = mx[i];
+        if (tq == 0) wmax[warp * ROWS + g + 8 * i] = mx[i];
       }
       __syncthreads();
-      float corr[2], m_new[2], ps[2] = {0.f, 0.f};
+      float corr[NR], m_new[NR], ps[NR];
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
+      for (int i = 0; i < NR; ++i) {
         const int r = g + 8 * i;
-        m_new[i] = fmaxf(fmaxf(fmaxf(wmax[r], wmax[16 + r]), fmaxf(wmax[32 + r], wmax[48 + r])), m_run[i]);
+        m_new[i] = fmaxf(fmaxf(fmaxf(wmax[r], wmax[ROWS + r]), fmaxf(wmax[2 * ROWS + r], wmax[3 * ROWS + r])), m_run[i]);
         corr[i] = __expf(m_run[i] - m_new[i]);
+        ps[i] = 0.f;
       }
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt) {
-        float p[4];
+      for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int i = e >> 1;
-          p[e] = s[nt][e] <= -1e29f ? 0.f : __expf(s[nt][e] - m_new[i]);
-          ps[i] += p[e];
+        for (int nt = 0; nt < 2; ++nt) {
+          float p[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i = mt * 2 + (e >> 1);
+            p[e] = s[mt][nt][e] <= -1e29f ? 0.f : __expf(s[mt][nt][e] - m_new[i]);
+            ps[i] += p[e];
+          }
+          const int col = warp * 16 + nt * 8 + 2 * tq;
+          *reinterpret_cast<uint32_t*>(Ps + (mt * 16 + g) * 72 + col) = pack_bf16(p[0], p[1]);
+          *reinterpret_cast<uint32_t*>(Ps + (mt * 16 + g + 8) * 72 + col) = pack_bf16(p[2], p[3]);
         }
-        const int col = warp * 16 + nt * 8 + 2 * tq;
-        *reinterpret_cast<uint32_t*>(Ps + g * 72 + col) = pack_bf16(p[0], p[1]);
-        *reinterpret_cast<uint32_t*>(Ps + (g + 8) * 72 + col) = pack_bf16(p[2], p[3]);
-      }
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
+      for (int i = 0; i < NR; ++i) {
         ps[i] += __shfl_xor_sync(0xffffffffu, ps[i], 1);
         ps[i] += __shfl_xor_sync(0xffffffffu, ps[i], 2);
-        if (tq == 0) wsum[warp * 16 + g + 8 * i] = ps[i];
+        if (tq == 0) wsum[warp * ROWS + g + 8 * i] = ps[i];
       }
       __syncthreads();
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
+      for (int i = 0; i < NR; ++i) {
         const int r = g + 8 * i;
-        l_run[i] = l_run[i] * corr[i] + (wsum[r] + wsum[16 + r]) + (wsum[32 + r] + wsum[48 + r]);
+        l_run[i] = l_run[i] * corr[i] + (wsum[r] + wsum[ROWS + r]) + (wsum[2 * ROWS + r] + wsum[3 * ROWS + r]);
         m_run[i] = m_new[i];
       }
 #pragma unroll
-      for (int n = 0; n < NV; ++n) {
-        o[n][0] *= corr[0];
-        o[n][1] *= corr[0];
-        o[n][2] *= corr[1];
-        o[n][3] *= corr[1];
-      }
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int n = 0; n < NV; ++n) {
+          o[mt][n][0] *= corr[2 * mt];
+          o[mt][n][1] *= corr[2 * mt];
+          o[mt][n][2] *= corr[2 * mt + 1];
+          o[mt][n][3] *= corr[2 * mt + 1];
+        }
       // ---- O += P V over this warp's output columns
       const int vcol0 = warp * (rank / 4);
 #pragma unroll
       for (int ks = 0; ks < kMmaKeys / 16; ++ks) {
-        uint32_t a[4];
-        ldsm_x4(a, Ps + ((lane & 7) + ((lane >> 3) & 1) * 8) * 72 + ks * 16 + ((lane >> 4) & 1) * 8);
+        uint32_t a[MT][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+          ldsm_x4(a[mt], Ps + (mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * 72 + ks * 16 + ((lane >> 4) & 1) * 8);
 #pragma unroll
         for (int np = 0; np < NV / 2; ++np) {
           if (np * 2 < nv) {
             uint32_t b[4];
             ldsm_x4_trans(b, Kt + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldk + vcol0 + np * 16 + ((lane >> 4) & 1) * 8);
-            mma_bf16_16816(o[2 * np], a, b[0], b[1]);
-            mma_bf16_16816(o[2 * np + 1], a, b[2], b[3]);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              mma_bf16_16816(o[mt][2 * np], a[mt], b[0], b[1]);
+              mma_bf16_16816(o[mt][2 * np + 1], a[mt], b[2], b[3]);
+            }
           }
         }
       }
@@ -185,8 +215,8 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, const bf16* __restrict_
   // ---- write: final rows (one split) or partial state (several)
   const int vcol0 = warp * (rank / 4);
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int r = g + 8 * i, R = R0 + r;
+  for (int i = 0; i < NR; ++i) {
+    const int r = g + 8 * i, R = R0 + r, mt = i >> 1, hf = i & 1;
     if (R >= total_rows) continue;
     if (nsplit == 1) {
       const float sk = bf2f(sink[R % heads]);
@@ -196,56 +226,64 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, const bf16* __restrict_
 #pragma unroll
       for (int n = 0; n < NV; ++n)
         if (n < nv)
-          *reinterpret_cast<uint32_t*>(out + (size_t)R * rank + vcol0 + n * 8 + 2 * tq) = pack_bf16(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
+          *reinterpret_cast<uint32_t*>(out + (size_t)R * rank + vcol0 + n * 8 + 2 * tq) = pack_bf16(o[mt][n][2 * hf] * inv, o[mt][n][2 * hf + 1] * inv);
     } else {
-      const size_t slot = ((size_t)blockIdx.x * nsplit + split) * kMmaRows + r;
+      const size_t slot = ((size_t)blockIdx.x * nsplit + split) * ROWS + r;
       if (warp == 0 && tq == 0) {
         part_ml[slot * 2] = m_run[i];
         part_ml[slot * 2 + 1] = l_run[i];
       }
 #pragma unroll
       for (int n = 0; n < NV; ++n)
-        if (n < nv) *reinterpret_cast<float2*>(part_o + slot * rank + vcol0 + n * 8 + 2 * tq) = make_float2(o[n][2 * i], o[n][2 * i + 1]);
+        if (n < nv) *reinterpret_cast<float2*>(part_o + slot * rank + vcol0 + n * 8 + 2 * tq) = make_float2(o[mt][n][2 * hf], o[mt][n][2 * hf + 1]);
     }
   }
 }
 
 // one block per query row: combine the splits' (m, l, O) and the sink
 __global__ void latent_attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const bf16* __restrict__ sink,
-                                              bf16* __restrict__ out, int nsplit, int heads, int rank) {
+                                              bf16* __restrict__ out, int nsplit, int heads, int rank, int tile_rows) {
+  __shared__ float wgt[64];  // per split: exp(m_s - M) / denominator
   pdl_wait();
-  const int R = blockIdx.x, tile = R / kMmaRows, r = R % kMmaRows;
-  const float sk = bf2f(sink[R % heads]);
-  float M = sk;
-  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, part_ml[(((size_t)tile * nsplit + s) * kMmaRows + r) * 2]);
-  float den = __expf(sk - M);
-  for (int s = 0; s < nsplit; ++s) {
-    const size_t slot = ((size_t)tile * nsplit + s) * kMmaRows + r;
-    den += part_ml[slot * 2 + 1] * __expf(part_ml[slot * 2] - M);
+  const int R = blockIdx.x, tile = R / tile_rows, r = R % tile_rows;
+  const size_t slot0 = (size_t)tile * nsplit * tile_rows + r;  // split s at slot0 + s * tile_rows
+  if (threadIdx.x < 32) {
+    const float sk = bf2f(sink[R % heads]);
+    float m[2], l[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int s = threadIdx.x + 32 * i;
+      m[i] = s < nsplit ? part_ml[(slot0 + (size_t)s * tile_rows) * 2] : kNegBig;
+      l[i] = s < nsplit ? part_ml[(slot0 + (size_t)s * tile_rows) * 2 + 1] : 0.f;
+    }
+    const float M = fmaxf(warp_max(fmaxf(m[0], m[1])), sk);
+    const float e0 = __expf(m[0] - M), e1 = __expf(m[1] - M);
+    const float inv = 1.f / (warp_sum(l[0] * e0 + l[1] * e1) + __expf(sk - M));
+    wgt[threadIdx.x] = e0 * inv;
+    wgt[threadIdx.x + 32] = e1 * inv;
   }
-  const float inv = 1.f / den;
+  __syncthreads();
   for (int d = threadIdx.x; d < rank; d += blockDim.x) {
     float acc = 0.f;
-    for (int s = 0; s < nsplit; ++s) {
-      const size_t slot = ((size_t)tile * nsplit + s) * kMmaRows + r;
-      acc += part_o[slot * rank + d] * __expf(part_ml[slot * 2] - M);
-    }
-    out[(size_t)R * rank + d] = f2bf(acc * inv);
+    for (int s = 0; s < nsplit; ++s) acc = fmaf(part_o[(slot0 + (size_t)s * tile_rows) * rank + d], wgt[s], acc);
+    out[(size_t)R * rank + d] = f2bf(acc);
   }
 }
 
-template <int NV>
+template <int NV, int MT>
 static cudaError_t launch_mma(dim3 grid, size_t smem, cudaStream_t st, const bf16* qa, const bf16* cache, const bf16* sink, const int* pos, const int* req,
                               const int* page_off, const int* pages, bf16* out, float* po, float* pml, long page_stride, int page_size, int tokens,
                               int heads, int rank, int rot, float scale) {
   static bool attr_done = false;
   if (!attr_done) {
-    cudaFuncSetAttribute(latent_attention_mma_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(latent_attention_mma_kernel<NV, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     attr_done = true;
   }
-  return launch(latent_attention_mma_kernel<NV>, grid, dim3(kMmaThreads), smem, st, true, qa, cache, sink, pos, req, page_off, pages, out, po, pml,
+  return launch(latent_attention_mma_kernel<NV, MT>, grid, dim3(kMmaThreads), smem, st, true, qa, cache, sink, pos, req, page_off, pages, out, po, pml,
                 page_stride, page_size, tokens, heads, rank, rot, scale);
 }
+
+static size_t mma_smem_bytes(int rows, int D) { return (size_t)(rows + 2 * kMmaKeys) * (D + 8) * 2 + (size_t)rows * 72 * 2 + (size_t)8 * rows * 4; }
 
 // 0 = launched; -2 = shape / alignment outside this kernel (the caller runs the generic kernel)
 int launch_latent_attention_mma(const bf16* qa, const bf16* cache, const bf16* sink, const int* pos, const int* req, const int* page_off,
@@ -255,28 +293,42 @@ int launch_latent_attention_mma(const bf16* qa, const bf16* cache, const bf16* s
   if (rank % 64 || rot % 16 || rank > 512 || page_stride % 8 || (reinterpret_cast<uintptr_t>(qa) & 15) || (reinterpret_cast<uintptr_t>(cache) & 15) ||
       (reinterpret_cast<uintptr_t>(out) & 3))
     return -2;
-  const size_t smem = (size_t)(kMmaRows + 2 * kMmaKeys) * (D + 8) * 2 + kMmaRows * 72 * 2 + 128 * 4;
-  if (smem > 200 * 1024) return -2;
-  const int tiles = (tokens * heads + kMmaRows - 1) / kMmaRows;
+  if (mma_smem_bytes(16, D) > 200 * 1024) return -2;
+  // 32-row CTAs once there are enough rows to fill the GPU with them; 16-row CTAs (with the key axis split) for a decode step
+  const int total = tokens * heads;
+  const int mt = (total >= 32 * sm_count() && mma_smem_bytes(32, D) <= 200 * 1024) ? 2 : 1;
+  const int rows = 16 * mt;
+  const size_t smem = mma_smem_bytes(rows, D);
+  const int tiles = (total + rows - 1) / rows;
   int splits = 1;
   ThreadState& ts = tls();
   if (max_kv_len > 2 * kMmaKeys && tiles < 2 * sm_count() && ts.scratch) {
     splits = min(min((2 * sm_count() + tiles - 1) / tiles, (max_kv_len + 2 * kMmaKeys - 1) / (2 * kMmaKeys)), 64);
-    while (splits > 1 && (size_t)tiles * splits * kMmaRows * (rank + 2) * 4 > ts.scratch_bytes) --splits;
+    while (splits > 1 && (size_t)tiles * splits * rows * (rank + 2) * 4 > ts.scratch_bytes) --splits;
   }
   float* po = static_cast<float*>(ts.scratch);
-  float* pml = po ? po + (size_t)tiles * splits * kMmaRows * rank : nullptr;
+  float* pml = po ? po + (size_t)tiles * splits * rows * rank : nullptr;
   const dim3 grid(tiles, splits);
   const int nv = rank / 32;
   cudaError_t e;
-  if (nv <= 2) e = launch_mma<2>(grid, smem, st, qa, cache, sink, pos, req, page_off, pages, out, po, pml, page_stride, page_size, tokens, heads, rank, rot, scale);
-  else if (nv <= 4) e = launch_mma<4>(grid, smem, st, qa, cache, sink, pos, req, page_off, pages, out, po, pml, page_stride, page_size, tokens, heads, rank, rot, scale);
-  else if (nv <= 8) e = launch_mma<8>(grid, smem, st, qa, cache, sink, pos, req, page_off, pages, out, po, pml, page_stride, page_size, tokens, heads, rank, rot, scale);
-  else e = launch_mma<16>(grid, smem, st, qa, cache, sink, pos, req, page_off, pages, out, po, pml, page_stride, page_size, tokens, heads, rank, rot, scale);
+#define PK_LAUNCH_MMA(NVV, MTT) \
+  launch_mma<NVV, MTT>(grid, smem, st, qa, cache, sink, pos, req, page_off, pages, out, po, pml, page_stride, page_size, tokens, heads, rank, rot, scale)
+  if (mt == 2) {
+    if (nv <= 2) e = PK_LAUNCH_MMA(2, 2);
+    else if (nv <= 4) e = PK_LAUNCH_MMA(4, 2);
+    else if (nv <= 8) e = PK_LAUNCH_MMA(8, 2);
+    else e = PK_LAUNCH_MMA(16, 2);
+  } else {
+    if (nv <= 2) e = PK_LAUNCH_MMA(2, 1);
+    else if (nv <= 4) e = PK_LAUNCH_MMA(4, 1);
+    else if (nv <= 8) e = PK_LAUNCH_MMA(8, 1);
+    else e = PK_LAUNCH_MMA(16, 1);
+  }
+#undef PK_LAUNCH_MMA
   if (e != cudaSuccess) return (int)e;
   if (splits > 1)
-    e = launch(latent_attention_merge_kernel, dim3(tokens * heads), dim3(128), 0, st, true, (const float*)po, (const float*)pml, sink, out, splits, heads,
-               rank);
+    e = launch(latent_attention_merge_kernel, dim3(total), dim3(128), 0, st, true, (const float*)po, (const float*)pml, sink, out, splits, heads, rank,
+               rows);
   return (int)e;
 }
 

@@ -98,7 +98,7 @@ constexpr int kMoeRowsPerBlock = 32;  // weight rows per CTA: a decode step spre
 template <typename E>
 __global__ void moe_up_kernel(const E* __restrict__ xa, const E* __restrict__ w_up, const int* __restrict__ ids, E* __restrict__ hid, int width,
                               int ff) {
-  extern __shared__ float xs[];
+  extern __shared__ __align__(16) float xs[];
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int tok = blockIdx.x, k = blockIdx.y, top = gridDim.y;
@@ -107,10 +107,7 @@ __global__ void moe_up_kernel(const E* __restrict__ xa, const E* __restrict__ w_
   const E* W = w_up + (size_t)ids[(size_t)tok * top + k] * ff * width;
   const int f_end = min(ff, (int)(blockIdx.z + 1) * kMoeRowsPerBlock);
   for (int f = blockIdx.z * kMoeRowsPerBlock + warp; f < f_end; f += nw) {
-    const E* wr = W + (size_t)f * width;
-    float acc = 0.f;
-    for (int i = lane; i < width; i += 32) acc = fmaf(to_f(wr[i]), xs[i], acc);
-    acc = warp_sum(acc);
+    const float acc = warp_dot(W + (size_t)f * width, xs, width, lane);
     if (lane == 0) {
       const float u = fmaxf(acc, 0.f);
       hid[((size_t)tok * top + k) * ff + f] = from_f<E>(u * u);
@@ -122,10 +119,11 @@ __global__ void moe_up_kernel(const E* __restrict__ xa, const E* __restrict__ w_
 template <typename E>
 __global__ void moe_down_kernel(const E* __restrict__ hid, const E* __restrict__ w_down, const int* __restrict__ ids, const float* __restrict__ wts,
                                 const E* __restrict__ shared, const float* __restrict__ sg, float* __restrict__ y, int width, int ff, int top) {
-  extern __shared__ float hs[];  // [top][ff]
+  extern __shared__ __align__(16) float hs[];  // [top][ffp], ffp = ff rounded up to 4 so that every row starts 16-byte aligned
   pdl_wait();
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  for (int i = threadIdx.x; i < top * ff; i += blockDim.x) hs[i] = to_f(hid[(size_t)t * top * ff + i]);
+  const int ffp = (ff + 3) & ~3;
+  for (int i = threadIdx.x; i < top * ff; i += blockDim.x) hs[(i / ff) * ffp + i % ff] = to_f(hid[(size_t)t * top * ff + i]);
   __syncthreads();
   const float g = shared ? 1.f / (1.f + expf(-sg[t])) : 0.f;
   const int i_end = min(width, (int)(blockIdx.y + 1) * kMoeRowsPerBlock);
@@ -133,9 +131,7 @@ __global__ void moe_down_kernel(const E* __restrict__ hid, const E* __restrict__
     float tot = 0.f;
     for (int k = 0; k < top; ++k) {
       const E* wr = w_down + ((size_t)ids[(size_t)t * top + k] * width + i) * ff;
-      float acc = 0.f;
-      for (int f = lane; f < ff; f += 32) acc = fmaf(to_f(wr[f]), hs[k * ff + f], acc);
-      tot = fmaf(wts[(size_t)t * top + k], warp_sum(acc), tot);
+      tot = fmaf(wts[(size_t)t * top + k], warp_dot(wr, hs + k * ffp, ff, lane), tot);
     }
     if (lane == 0) y[(size_t)t * width + i] = tot + (shared ? g * to_f(shared[(size_t)t * width + i]) : 0.f);
   }
@@ -169,7 +165,7 @@ extern "C" int pk_moe_up_relu2(const void* xa, const void* w_up, const int* ids,
 extern "C" int pk_moe_down_combine(const void* hid, const void* w_down, const int* ids, const float* weights, const void* shared,
                                    const float* shared_gate, float* y, int tokens, int top, int width, int ff, int f32, pk_stream st) {
   if (!hid || !w_down || !ids || !weights || !y || tokens <= 0 || top <= 0 || width <= 0 || ff <= 0 || (shared && !shared_gate)) return -1;
-  const size_t smem = (size_t)top * ff * sizeof(float);
+  const size_t smem = (size_t)top * ((ff + 3) & ~3) * sizeof(float);
   if (smem > 200 * 1024) return -2;
   if (f32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_down_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

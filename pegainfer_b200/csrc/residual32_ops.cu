@@ -67,10 +67,7 @@ __global__ void skinny_proj_kernel(const E* __restrict__ W, const float* __restr
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const float* xr = x + (size_t)t * K;
   for (int m = blockIdx.y * nw + warp; m < M; m += gridDim.y * nw) {
-    const E* wr = W + (size_t)m * K;
-    float acc = 0.f;
-    for (int k = lane; k < K; k += 32) acc = fmaf(to_f(wr[k]), xr[k], acc);
-    acc = warp_sum(acc);
+    const float acc = warp_dot(W + (size_t)m * K, xr, K, lane);
     if (lane == 0) out[(size_t)t * M + m] = acc;
   }
 }
@@ -165,6 +162,28 @@ __global__ void gemm_strided_kernel(const E* __restrict__ A, const E* __restrict
   }
 }
 
+// The same product for a few rows (decode) when B is K-contiguous (sbk == 1): grid (row, batch, slice of columns); the A row
+// is staged as fp32 in shared memory and every warp streams whole B rows.
+template <typename E>
+__global__ void gemm_strided_rows_kernel(const E* __restrict__ A, const E* __restrict__ B, E* __restrict__ C, const float* __restrict__ row_scale,
+                                         int cols, int K, long lda, long sbn, long ldc, long bsA, long bsB, long bsC, int ld_scale, int scale_kind) {
+  extern __shared__ __align__(16) float a_s[];
+  pdl_wait();
+  const int i = blockIdx.x, b = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const E* a = A + (size_t)b * bsA + (size_t)i * lda;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) a_s[k] = to_f(a[k]);
+  __syncthreads();
+  float s = 1.f;
+  if (row_scale) {
+    s = row_scale[(size_t)i * ld_scale + b];
+    if (scale_kind == 2) s = 1.f / (1.f + expf(-s));
+  }
+  for (int j = blockIdx.z * nw + warp; j < cols; j += gridDim.z * nw) {
+    const float acc = warp_dot(B + (size_t)b * bsB + (size_t)j * sbn, a_s, K, lane);
+    if (lane == 0) C[(size_t)b * bsC + (size_t)i * ldc + j] = from_f<E>(acc * s);
+  }
+}
+
 static inline int grid_1d(long n, int block) {
   long g = (n + block - 1) / block;
   return (int)(g < 1 ? 1 : (g > 148 * 16 ? 148 * 16 : g));
@@ -241,6 +260,16 @@ extern "C" int pk_convert(const void* in, int in_f32, void* out, int out_f32, lo
 extern "C" int pk_gemm_strided(const void* A, const void* B, void* C, const float* row_scale, int rows, int cols, int K, long lda, long sbk,
                                long sbn, long ldc, int batch, long bsA, long bsB, long bsC, int ld_scale, int scale_kind, int f32, pk_stream st) {
   if (!A || !B || !C || rows <= 0 || cols <= 0 || K <= 0 || batch <= 0) return -1;
+  if (rows <= 8 && sbk == 1 && K <= 8192) {
+    const dim3 gr(rows, batch, (cols + 31) / 32), br(256);
+    const size_t sm = (size_t)K * sizeof(float);
+    PK_BY_TYPE(f32,
+               launch(gemm_strided_rows_kernel<float>, gr, br, sm, st, true, (const float*)A, (const float*)B, (float*)C, row_scale, cols, K, lda, sbn,
+                      ldc, bsA, bsB, bsC, ld_scale, scale_kind),
+               launch(gemm_strided_rows_kernel<bf16>, gr, br, sm, st, true, (const bf16*)A, (const bf16*)B, (bf16*)C, row_scale, cols, K, lda, sbn, ldc,
+                      bsA, bsB, bsC, ld_scale, scale_kind));
+    return (int)cudaGetLastError();
+  }
   const dim3 g((cols + 63) / 64, (rows + 63) / 64, batch), b(256);
   PK_BY_TYPE(f32,
              launch(gemm_strided_kernel<float>, g, b, 0, st, true, (const float*)A, (const float*)B, (float*)C, row_scale, rows, cols, K, lda, sbk,

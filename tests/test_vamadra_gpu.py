@@ -285,6 +285,23 @@ def test_latent_attention_ragged_batch(lib, dtype, H, rank, rot_w):
     assert torch.allclose(got, want, atol=tol, rtol=tol)
 
 
+@pytest.mark.parametrize("H,rank,rot_w", [(16, 64, 16), (24, 128, 32)])
+def test_latent_attention_many_rows_take_the_wide_tiles(lib, H, rank, rot_w):
+    """enough query rows to fill the GPU with 32-row CTAs (bf16): a 201-token prompt beside a 110-token portion that starts at
+    position 40 of another request; the tile at the seam holds rows of both requests"""
+    g = torch.Generator().manual_seed(8)
+    lens = [201, 150]
+    c = [torch.randn(n, rank, generator=g).to(BF16).to(F32) for n in lens]
+    kr = [torch.randn(n, rot_w, generator=g).to(BF16).to(F32) for n in lens]
+    pos = list(range(201)) + list(range(40, 150))
+    req = [0] * 201 + [1] * 110
+    qa = (torch.randn(311, H, rank + rot_w, generator=g) * (2.0 / math.sqrt(rank / 40))).to(BF16).to(F32)
+    sink = torch.randn(H, generator=g).to(BF16).to(F32)
+    got = run_attention(lib, BF16, qa, c, kr, sink, pos, req, lens, 16, 0.2)
+    want = torch.cat([oracle_attention(qa[:201], c[0], kr[0], sink, pos[:201], 0.2), oracle_attention(qa[201:], c[1], kr[1], sink, pos[201:], 0.2)])
+    assert torch.allclose(got, want, atol=3e-2, rtol=3e-2)
+
+
 def test_latent_attention_few_rows_long_contexts_split_over_keys(lib):
     """decoded tokens of two requests with 3000 and 1500 cached positions (bf16, tensor-core kernel): the key axis is split over
     CTAs and merged; one key far back carries most of the weight for one head"""
