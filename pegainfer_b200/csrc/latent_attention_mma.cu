@@ -15,18 +15,19 @@
 
 namespace pk {
 
-constexpr int kMmaKeys = 64, kMmaThreads = 128;
+constexpr int kMmaKeys = 64;
 constexpr float kNegBig = -1e30f;
 
-// NV = 8-column output tiles per warp (rank = 32 * nv with nv <= NV, nv even); MT = 16-row query tiles per CTA (2 for prompt
-// portions: every fetched key tile and every K / V fragment then serves 32 rows; 1 for the few rows of a decode step)
-template <int NV, int MT>
-__global__ void __launch_bounds__(kMmaThreads)
+// NV = 8-column output tiles per warp (rank = 32 * nv with nv <= NV, nv even); MT = 16-row query tiles per warp group;
+// WG = groups of 4 warps, each with its own MT tiles, sharing the fetched key tiles (2 for prompt portions: twice the rows per
+// key fetch and two warps per scheduler to hide each other's latencies; 1 for the few rows of a decode step)
+template <int NV, int MT, int WG>
+__global__ void __launch_bounds__(128 * WG)
 latent_attention_mma_kernel(const bf16* __restrict__ qa, const bf16* __restrict__ cache, const bf16* __restrict__ sink, const int* __restrict__ pos,
                             const int* __restrict__ req, const int* __restrict__ page_off, const int* __restrict__ pages, bf16* __restrict__ out,
                             float* __restrict__ part_o, float* __restrict__ part_ml, long page_stride, int page_size, int tokens, int heads, int rank,
                             int rot, float scale) {
-  constexpr int ROWS = 16 * MT, NR = 2 * MT;  // NR = rows per thread: g + 8 * i, i < NR
+  constexpr int ROWS_G = 16 * MT, ROWS = ROWS_G * WG, NR = 2 * MT;  // NR = rows per thread: rb + g + 8 * i, i < NR
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int D = rank + rot, ldk = D + 8, nv = rank / 32;
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);   // [ROWS][ldk]
@@ -34,14 +35,15 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, const bf16* __restrict_
   bf16* Ps = Ks + 2 * kMmaKeys * ldk;             // [ROWS][72]
   float* wmax = reinterpret_cast<float*>(Ps + ROWS * 72);  // [4][ROWS]
   float* wsum = wmax + 4 * ROWS;                           // [4][ROWS]
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tq = lane & 3;
+  const int tid = threadIdx.x, lane = tid & 31, warp = (tid >> 5) & 3, rb = (tid >> 7) * ROWS_G, g = lane >> 2, tq = lane & 3;
+  const int nthreads = 128 * WG;
   const int total_rows = tokens * heads, R0 = blockIdx.x * ROWS;
   const int split = blockIdx.y, nsplit = gridDim.y;
   pdl_wait();
 
   // ---- Q tile (rows past the end are zero)
   const int chunks = D / 8;  // 16-byte pieces per row
-  for (int e = tid; e < ROWS * chunks; e += kMmaThreads) {
+  for (int e = tid; e < ROWS * chunks; e += nthreads) {
     const int r = e / chunks, c = e % chunks;
     bf16* dst = Qs + r * ldk + c * 8;
     if (R0 + r < total_rows) cp_async16(dst, qa + (size_t)(R0 + r) * D + c * 8);
@@ -49,10 +51,12 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, const bf16* __restrict_
   }
   cp_async_commit();
 
+  const int ld_r0 = tid / chunks, ld_c0 = tid % chunks, ld_dr = nthreads / chunks, ld_dc = nthreads % chunks;
+  const int ps_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
   int row_tok[NR], row_pos[NR];
 #pragma unroll
   for (int i = 0; i < NR; ++i) {
-    const int R = R0 + g + 8 * i;
+    const int R = R0 + rb + g + 8 * i;
     row_tok[i] = R < total_rows ? R / heads : -1;
     row_pos[i] = row_tok[i] >= 0 ? pos[row_tok[i]] : -1;
   }
@@ -84,11 +88,23 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, const bf16* __restrict_
 
     auto load_keys = [&](int j0, int buf) {
       bf16* base = Ks + (size_t)buf * kMmaKeys * ldk;
-      for (int e = tid; e < kMmaKeys * chunks; e += kMmaThreads) {
-        const int r = e / chunks, c = e % chunks, j = j0 + r;
+      int r = ld_r0, c = ld_c0;  // (key row, 16-byte piece) of this thread's first piece; the next one is nthreads pieces on
+      while (r < kMmaKeys) {
+        const int j = j0 + r;
         bf16* dst = base + r * ldk + c * 8;
-        if (j < k_end) cp_async16(dst, cache + (size_t)pg[j / page_size] * page_stride + (size_t)(j % page_size) * D + c * 8);
-        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        if (j < k_end) {
+          const int page = ps_shift >= 0 ? pg[j >> ps_shift] : pg[j / page_size];
+          const int slot = ps_shift >= 0 ? (j & (page_size - 1)) : j % page_size;
+          cp_async16(dst, cache + (size_t)page * page_stride + (size_t)slot * D + c * 8);
+        } else {
+          *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
+        r += ld_dr;
+        c += ld_dc;
+        if (c >= chunks) {
+          c -= chunks;
+          ++r;
+        }
       }
       cp_async_commit();
     };
@@ -114,7 +130,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, const bf16* __restrict_
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
           uint32_t a[4];
-          ldsm_x4(a, Qs + (mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldk + kk + ((lane >> 4) & 1) * 8);
+          ldsm_x4(a, Qs + (rb + mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldk + kk + ((lane >> 4) & 1) * 8);
           mma_bf16_16816(s[mt][0], a, b[0], b[1]);
           mma_bf16_16816(s[mt][1], a, b[2], b[3]);
         }
@@ -137,13 +153,13 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, const bf16* __restrict_
       for (int i = 0; i < NR; ++i) {
         mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
         mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
-        if (tq == 0) wmax[warp * ROWS + g + 8 * i] = mx[i];
+        if (tq == 0) wmax[warp * ROWS + rb + g + 8 * i] = mx[i];
       }
       __syncthreads();
       float corr[NR], m_new[NR], ps[NR];
 #pragma unroll
       for (int i = 0; i < NR; ++i) {
-        const int r = g + 8 * i;
+        const int r = rb + g + 8 * i;
         m_new[i] = fmaxf(fmaxf(fmaxf(wmax[r], wmax[ROWS + r]), fmaxf(wmax[2 * ROWS + r], wmax[3 * ROWS + r])), m_run[i]);
         corr[i] = __expf(m_run[i] - m_new[i]);
         ps[i] = 0.f;
@@ -160,19 +176,19 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, const bf16* __restrict_
             ps[i] += p[e];
           }
           const int col = warp * 16 + nt * 8 + 2 * tq;
-          *reinterpret_cast<uint32_t*>(Ps + (mt * 16 + g) * 72 + col) = pack_bf16(p[0], p[1]);
-          *reinterpret_cast<uint32_t*>(Ps + (mt * 16 + g + 8) * 72 + col) = pack_bf16(p[2], p[3]);
+          *reinterpret_cast<uint32_t*>(Ps + (rb + mt * 16 + g) * 72 + col) = pack_bf16(p[0], p[1]);
+          *reinterpret_cast<uint32_t*>(Ps + (rb + mt * 16 + g + 8) * 72 + col) = pack_bf16(p[2], p[3]);
         }
 #pragma unroll
       for (int i = 0; i < NR; ++i) {
         ps[i] += __shfl_xor_sync(0xffffffffu, ps[i], 1);
         ps[i] += __shfl_xor_sync(0xffffffffu, ps[i], 2);
-        if (tq == 0) wsum[warp * ROWS + g + 8 * i] = ps[i];
+        if (tq == 0) wsum[warp * ROWS + rb + g + 8 * i] = ps[i];
       }
       __syncthreads();
 #pragma unroll
       for (int i = 0; i < NR; ++i) {
-        const int r = g + 8 * i;
+        const int r = rb + g + 8 * i;
         l_run[i] = l_run[i] * corr[i] + (wsum[r] + wsum[ROWS + r]) + (wsum[2 * ROWS + r] + wsum[3 * ROWS + r]);
         m_run[i] = m_new[i];
       }
@@ -192,7 +208,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, const bf16* __restrict_
         uint32_t a[MT][4];
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
-          ldsm_x4(a[mt], Ps + (mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * 72 + ks * 16 + ((lane >> 4) & 1) * 8);
+          ldsm_x4(a[mt], Ps + (rb + mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * 72 + ks * 16 + ((lane >> 4) & 1) * 8);
 #pragma unroll
         for (int np = 0; np < NV / 2; ++np) {
           if (np * 2 < nv) {
@@ -216,7 +232,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, const bf16* __restrict_
   const int vcol0 = warp * (rank / 4);
 #pragma unroll
   for (int i = 0; i < NR; ++i) {
-    const int r = g + 8 * i, R = R0 + r, mt = i >> 1, hf = i & 1;
+    const int r = rb + g + 8 * i, R = R0 + r, mt = i >> 1, hf = i & 1;
     if (R >= total_rows) continue;
     if (nsplit == 1) {
       const float sk = bf2f(sink[R % heads]);
@@ -270,16 +286,16 @@ __global__ void latent_attention_merge_kernel(const float* __restrict__ part_o, 
   }
 }
 
-template <int NV, int MT>
+template <int NV, int MT, int WG>
 static cudaError_t launch_mma(dim3 grid, size_t smem, cudaStream_t st, const bf16* qa, const bf16* cache, const bf16* sink, const int* pos, const int* req,
                               const int* page_off, const int* pages, bf16* out, float* po, float* pml, long page_stride, int page_size, int tokens,
                               int heads, int rank, int rot, float scale) {
   static bool attr_done = false;
   if (!attr_done) {
-    cudaFuncSetAttribute(latent_attention_mma_kernel<NV, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(latent_attention_mma_kernel<NV, MT, WG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     attr_done = true;
   }
-  return launch(latent_attention_mma_kernel<NV, MT>, grid, dim3(kMmaThreads), smem, st, true, qa, cache, sink, pos, req, page_off, pages, out, po, pml,
+  return launch(latent_attention_mma_kernel<NV, MT, WG>, grid, dim3(128 * WG), smem, st, true, qa, cache, sink, pos, req, page_off, pages, out, po, pml,
                 page_stride, page_size, tokens, heads, rank, rot, scale);
 }
 
@@ -294,10 +310,10 @@ int launch_latent_attention_mma(const bf16* qa, const bf16* cache, const bf16* s
       (reinterpret_cast<uintptr_t>(out) & 3))
     return -2;
   if (mma_smem_bytes(16, D) > 200 * 1024) return -2;
-  // 32-row CTAs once there are enough rows to fill the GPU with them; 16-row CTAs (with the key axis split) for a decode step
+  // 32-row CTAs (two warp groups) once there are enough rows to fill the GPU with them; 16-row CTAs, key axis split, for a decode step
   const int total = tokens * heads;
-  const int mt = (total >= 32 * sm_count() && mma_smem_bytes(32, D) <= 200 * 1024) ? 2 : 1;
-  const int rows = 16 * mt;
+  const int wg = (total >= 32 * sm_count() && mma_smem_bytes(32, D) <= 200 * 1024) ? 2 : 1;
+  const int rows = 16 * wg;
   const size_t smem = mma_smem_bytes(rows, D);
   const int tiles = (total + rows - 1) / rows;
   int splits = 1;
@@ -311,9 +327,9 @@ int launch_latent_attention_mma(const bf16* qa, const bf16* cache, const bf16* s
   const dim3 grid(tiles, splits);
   const int nv = rank / 32;
   cudaError_t e;
-#define PK_LAUNCH_MMA(NVV, MTT) \
-  launch_mma<NVV, MTT>(grid, smem, st, qa, cache, sink, pos, req, page_off, pages, out, po, pml, page_stride, page_size, tokens, heads, rank, rot, scale)
-  if (mt == 2) {
+#define PK_LAUNCH_MMA(NVV, WGG) \
+  launch_mma<NVV, 1, WGG>(grid, smem, st, qa, cache, sink, pos, req, page_off, pages, out, po, pml, page_stride, page_size, tokens, heads, rank, rot, scale)
+  if (wg == 2) {
     if (nv <= 2) e = PK_LAUNCH_MMA(2, 2);
     else if (nv <= 4) e = PK_LAUNCH_MMA(4, 2);
     else if (nv <= 8) e = PK_LAUNCH_MMA(8, 2);

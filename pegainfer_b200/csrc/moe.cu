@@ -92,6 +92,7 @@ __global__ void router_grouped_topk_kernel(const float* __restrict__ z, int* __r
   if (lane < top) wts[(size_t)t * top + lane] = wts[(size_t)t * top + lane] / (total + 1e-20f) * scale;
 }
 
+constexpr int kMoeDownRowsPerBlock = 8;  // one output row per warp: each row already streams `top` weight rows
 constexpr int kMoeRowsPerBlock = 32;  // weight rows per CTA: a decode step spreads one expert over many SMs
 
 // hid[t, k, f] = act(W_up[ids[t,k]][f] . x[t]); act = relu^2.  Grid (token, choice, slice of ff rows).
@@ -126,8 +127,8 @@ __global__ void moe_down_kernel(const E* __restrict__ hid, const E* __restrict__
   for (int i = threadIdx.x; i < top * ff; i += blockDim.x) hs[(i / ff) * ffp + i % ff] = to_f(hid[(size_t)t * top * ff + i]);
   __syncthreads();
   const float g = shared ? 1.f / (1.f + expf(-sg[t])) : 0.f;
-  const int i_end = min(width, (int)(blockIdx.y + 1) * kMoeRowsPerBlock);
-  for (int i = blockIdx.y * kMoeRowsPerBlock + warp; i < i_end; i += nw) {
+  const int i_end = min(width, (int)(blockIdx.y + 1) * kMoeDownRowsPerBlock);
+  for (int i = blockIdx.y * kMoeDownRowsPerBlock + warp; i < i_end; i += nw) {
     float tot = 0.f;
     for (int k = 0; k < top; ++k) {
       const E* wr = w_down + ((size_t)ids[(size_t)t * top + k] * width + i) * ff;
@@ -169,11 +170,11 @@ extern "C" int pk_moe_down_combine(const void* hid, const void* w_down, const in
   if (smem > 200 * 1024) return -2;
   if (f32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_down_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    launch(moe_down_kernel<float>, dim3(tokens, (width + kMoeRowsPerBlock - 1) / kMoeRowsPerBlock), dim3(256), smem, st, true, (const float*)hid, (const float*)w_down, ids, weights,
+    launch(moe_down_kernel<float>, dim3(tokens, (width + kMoeDownRowsPerBlock - 1) / kMoeDownRowsPerBlock), dim3(256), smem, st, true, (const float*)hid, (const float*)w_down, ids, weights,
            (const float*)shared, shared_gate, y, width, ff, top);
   } else {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_down_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    launch(moe_down_kernel<bf16>, dim3(tokens, (width + kMoeRowsPerBlock - 1) / kMoeRowsPerBlock), dim3(256), smem, st, true, (const bf16*)hid, (const bf16*)w_down, ids, weights, (const bf16*)shared,
+    launch(moe_down_kernel<bf16>, dim3(tokens, (width + kMoeDownRowsPerBlock - 1) / kMoeDownRowsPerBlock), dim3(256), smem, st, true, (const bf16*)hid, (const bf16*)w_down, ids, weights, (const bf16*)shared,
            shared_gate, y, width, ff, top);
   }
   return (int)cudaGetLastError();
