@@ -43,7 +43,7 @@ def _run(cmd: list[str]) -> None:
 # What one design needs when nothing is built yet (a fresh checkout asked to serve that design compiles these files and no
 # others): kernel sources, host sources.  A later full build adds the rest and links both libraries again.
 PARTS_OF = {
-    "Vamadra": (("runtime.cu", "gemm.cu", "gemm2.cu", "gemv.cu", "sampling.cu", "residual32_ops.cu", "latent_attention.cu", "latent_attention_mma.cu", "moe.cu", "moe_grouped.cu"),
+    "Vamadra": (("runtime.cu", "gemm.cu", "gemm2.cu", "gemv.cu", "sampling.cu", "residual32_ops.cu", "gemm_batched_mma.cu", "latent_attention.cu", "latent_attention_mma.cu", "moe.cu", "moe_grouped.cu"),
                 ("qwen3_host.cpp", "vamadra_host.cpp")),
 }
 MANIFEST = os.path.join(OBJ, "linked.txt")

@@ -18,8 +18,10 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <map>
 #include <set>
 #include <string>
+#include <tuple>
 
 #include "qwen3_host.hpp"
 
@@ -74,6 +76,7 @@ struct Lib {
   }
 };
 
+static const int kGraphCtxBucket = 512;   // captured decode steps are keyed by the context length rounded up to this
 static const int kGroupedMinTokens = 32;  // from this many tokens in a step the experts run bucketed
 
 struct Mat {
@@ -115,6 +118,11 @@ struct Model {
   int* sampled_h = nullptr;
   bool keep_trail = false;
   int trail_tokens = 0;
+  // captured decode steps
+  typedef std::tuple<int, int, int, int> GraphKey;  // entries, logits rows, sampling, context bucket
+  std::map<GraphKey, cudaGraphExec_t> graphs;
+  std::set<GraphKey> seen;
+  bool use_graph = true;
   // widest layer
   int mx_q = 0, mx_dkv = 0, mx_qa = 0, mx_h = 0, mx_olat = 0, mx_ao = 0, mx_gu = 0, mx_act = 0, mx_e = 0, mx_top = 0, mx_hid = 0;
 
@@ -134,6 +142,7 @@ struct Model {
   }
   ~Model() {
     if (st) cudaStreamSynchronize(st);
+    drop_graphs();
     if (meta_h) cudaFreeHost(meta_h);
     if (sampled_h) cudaFreeHost(sampled_h);
     if (k.cublas_destroy) k.cublas_destroy();
@@ -146,7 +155,14 @@ struct Model {
   bool ensure_scratch(int T, int R);
   bool lin(const Mat& W, const void* X, void* Y, int N);
   bool run_layer(int li, int T, int max_kv, const int* d_pos, const int* d_req, const int* d_poff, const int* d_pages);
+  bool forward(int T, int n, int n_rows, int max_kv, int want_sample);
   bool step(int n, const int* tokens, const int* lens, const int* rids, int n_rows, const int* rows, int want_sample);
+  void drop_graphs() {
+    for (auto& g : graphs)
+      if (g.second) cudaGraphExecDestroy(g.second);
+    graphs.clear();
+    seen.clear();
+  }
 };
 
 static std::string lname(int i, const char* s) { return "l" + std::to_string(i) + "." + s; }
@@ -347,6 +363,7 @@ bool Model::ensure_scratch(int T, int R) {
   bool ok = true;
   if (T > cap_t) {
     cudaStreamSynchronize(st);
+    drop_graphs();
     const size_t n = ((size_t)T + 63) / 64 * 64, W = c.width;
     ok = x.alloc_uninit(n * W * 4) && xa.alloc_uninit(n * W * es) && q.alloc_uninit(n * mx_q * es) && dkv.alloc_uninit(n * mx_dkv * es) &&
          qa.alloc_uninit(n * mx_qa * es) && gate.alloc_uninit(n * mx_h * 4) && olat.alloc_uninit(n * mx_olat * es) &&
@@ -364,6 +381,7 @@ bool Model::ensure_scratch(int T, int R) {
   }
   if (ok && R > cap_r) {
     cudaStreamSynchronize(st);
+    drop_graphs();
     const size_t n = ((size_t)R + 15) / 16 * 16;
     ok = xr.alloc_uninit(n * c.width * es) && logits_e.alloc_uninit(n * c.vocab * es) && logits_f.alloc_uninit(n * c.vocab * 4) &&
          logits_bf.alloc_uninit(n * c.vocab * 2) && sampled_d.alloc_zeros(n * 4);
@@ -454,6 +472,32 @@ bool Model::run_layer(int li, int T, int max_kv, const int* d_pos, const int* d_
   return true;
 }
 
+// everything between the metadata upload and the final synchronisation: launches only (no allocation, no synchronisation)
+bool Model::forward(int T, int n, int n_rows, int max_kv, int want_sample) {
+  const int* M = meta_d.i32();
+  const int *d_tok = M, *d_pos = M + T, *d_req = M + 2 * T, *d_poff = M + 3 * T, *d_rows = M + 3 * T + n, *d_pages = M + 3 * T + n + n_rows;
+  if (!rc(k.pk_res32_embed(embed.d.ptr, d_tok, (float*)x.ptr, xa.ptr, c.width, T, c.f32, st), "embedding")) return false;
+  for (int li = 0; li < c.n_layers; ++li)
+    if (!run_layer(li, T, max_kv, d_pos, d_req, d_poff, d_pages)) return false;
+  if (n_rows > 0) {
+    if (!rc(k.pk_res32_offset_norm_rows((const float*)x.ptr, d_rows, final_norm.d.ptr, xr.ptr, c.width, n_rows, c.eps, c.f32, st), "final norm"))
+      return false;
+    if (!lin(head, xr.ptr, logits_e.ptr, n_rows)) return false;
+    if (!rc(k.pk_convert(logits_e.ptr, c.f32, logits_f.ptr, 1, (long)n_rows * c.vocab, st), "logits")) return false;
+    if (want_sample) {
+      const pk_bf16* lb = (const pk_bf16*)logits_e.ptr;
+      if (c.f32) {
+        if (!rc(k.pk_convert(logits_e.ptr, 1, logits_bf.ptr, 0, (long)n_rows * c.vocab, st), "logits")) return false;
+        lb = (const pk_bf16*)logits_bf.ptr;
+      }
+      for (int i = 0; i < n_rows; ++i)
+        k.flashinfer_top1_cuda(lb + (size_t)i * c.vocab, (pk_bf16*)top1_val.ptr, (uint8_t*)top1_states.ptr, sampled_d.i32() + i, c.vocab, st);
+      if (!cu(cudaMemcpyAsync(sampled_h, sampled_d.ptr, (size_t)std::min(n_rows, 1024) * 4, cudaMemcpyDeviceToHost, st), "sampled tokens")) return false;
+    }
+  }
+  return true;
+}
+
 // One engine step over a ragged batch.  tokens: all entries' tokens back to back; lens[i] tokens belong to request rids[i];
 // rows: indices into that flat token list whose logits are wanted.  Leaves fp32 logits [n_rows, vocab] in logits_f (and the
 // greedy token of each row in sampled_h when want_sample).
@@ -521,6 +565,7 @@ bool Model::step(int n, const int* tokens, const int* lens, const int* rids, int
   meta.insert(meta.end(), page_list.begin(), page_list.end());
   if (meta.size() > meta_cap) {
     cudaStreamSynchronize(st);
+    drop_graphs();
     if (meta_h) cudaFreeHost(meta_h);
     meta_cap = meta.size() * 2 + 1024;
     if (cudaMallocHost((void**)&meta_h, meta_cap * 4) != cudaSuccess || !meta_d.alloc_uninit(meta_cap * 4)) {
@@ -531,27 +576,39 @@ bool Model::step(int n, const int* tokens, const int* lens, const int* rids, int
   }
   memcpy(meta_h, meta.data(), meta.size() * 4);
   if (!cu(cudaMemcpyAsync(meta_d.ptr, meta_h, meta.size() * 4, cudaMemcpyHostToDevice, st), "metadata upload")) return false;
-  const int* M = meta_d.i32();
-  const int *d_tok = M, *d_pos = M + T, *d_req = M + 2 * T, *d_poff = M + 3 * T, *d_rows = M + 3 * T + n, *d_pages = M + 3 * T + n + n_rows;
-  if (!rc(k.pk_res32_embed(embed.d.ptr, d_tok, (float*)x.ptr, xa.ptr, c.width, T, c.f32, st), "embedding")) return false;
-  for (int li = 0; li < c.n_layers; ++li)
-    if (!run_layer(li, T, max_kv, d_pos, d_req, d_poff, d_pages)) return false;
-  if (n_rows > 0) {
-    if (!rc(k.pk_res32_offset_norm_rows((const float*)x.ptr, d_rows, final_norm.d.ptr, xr.ptr, c.width, n_rows, c.eps, c.f32, st), "final norm"))
-      return false;
-    if (!lin(head, xr.ptr, logits_e.ptr, n_rows)) return false;
-    if (!rc(k.pk_convert(logits_e.ptr, c.f32, logits_f.ptr, 1, (long)n_rows * c.vocab, st), "logits")) return false;
-    if (want_sample) {
-      const pk_bf16* lb = (const pk_bf16*)logits_e.ptr;
-      if (c.f32) {
-        if (!rc(k.pk_convert(logits_e.ptr, 1, logits_bf.ptr, 0, (long)n_rows * c.vocab, st), "logits")) return false;
-        lb = (const pk_bf16*)logits_bf.ptr;
+  // Decode steps (one token per entry) repeat with the same shapes: the launch sequence is captured once per (entries, rows,
+  // sampling, context bucket) and replayed; only the metadata block changes.  The first step of a kind runs eagerly (it also
+  // lets every kernel set its attributes outside a capture).
+  bool single = use_graph && !keep_trail && T == n;
+  bool ok;
+  if (single) {
+    const int bucket = (max_kv + kGraphCtxBucket - 1) / kGraphCtxBucket;
+    const GraphKey key{n, n_rows, want_sample, bucket};
+    auto it = graphs.find(key);
+    if (it != graphs.end()) {
+      ok = cu(cudaGraphLaunch(it->second, st), "graph launch");
+    } else if (seen.count(key)) {
+      ok = cu(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal), "begin capture");
+      if (ok) {
+        const bool body_ok = forward(T, n, n_rows, bucket * kGraphCtxBucket, want_sample);
+        cudaGraph_t gr = nullptr;
+        const cudaError_t e = cudaStreamEndCapture(st, &gr);
+        cudaGraphExec_t ex = nullptr;
+        ok = body_ok && cu(e, "end capture") && cu(cudaGraphInstantiate(&ex, gr, 0), "graph instantiate");
+        if (gr) cudaGraphDestroy(gr);
+        if (ok) {
+          graphs[key] = ex;
+          ok = cu(cudaGraphLaunch(ex, st), "graph launch");
+        }
       }
-      for (int i = 0; i < n_rows; ++i)
-        k.flashinfer_top1_cuda(lb + (size_t)i * c.vocab, (pk_bf16*)top1_val.ptr, (uint8_t*)top1_states.ptr, sampled_d.i32() + i, c.vocab, st);
-      if (!cu(cudaMemcpyAsync(sampled_h, sampled_d.ptr, (size_t)std::min(n_rows, 1024) * 4, cudaMemcpyDeviceToHost, st), "sampled tokens")) return false;
+    } else {
+      seen.insert(key);
+      ok = forward(T, n, n_rows, bucket * kGraphCtxBucket, want_sample);
     }
+  } else {
+    ok = forward(T, n, n_rows, max_kv, want_sample);
   }
+  if (!ok) return false;
   if (!cu(cudaStreamSynchronize(st), "step")) return false;
   txn.committed = true;
   return true;
@@ -636,6 +693,8 @@ PV_API int pv_step(void* mp, int n, const int* tokens, const int* lens, const in
   return 0;
 }
 PV_API void pv_keep_trail(void* mp, int on) { PV_M->keep_trail = on != 0; }
+PV_API void pv_use_graph(void* mp, int on) { PV_M->use_graph = on != 0; }
+PV_API int pv_graph_count(void* mp) { return (int)PV_M->graphs.size(); }
 // residual stream after every layer of the last step, [layers, tokens, width] fp32
 PV_API int pv_copy_trail(void* mp, float* host_out) {
   pv::Model* m = PV_M;

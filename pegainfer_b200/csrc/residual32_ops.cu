@@ -184,6 +184,10 @@ __global__ void gemm_strided_rows_kernel(const E* __restrict__ A, const E* __res
   }
 }
 
+// gemm_batched_mma.cu
+int launch_gemm_batched_mma(const bf16* A, const bf16* B, bf16* C, const float* row_scale, int rows, int cols, int K, long lda, long ldb, long ldc,
+                            int batch, long bsA, long bsB, long bsC, int ld_scale, int scale_kind, cudaStream_t st);
+
 static inline int grid_1d(long n, int block) {
   long g = (n + block - 1) / block;
   return (int)(g < 1 ? 1 : (g > 148 * 16 ? 148 * 16 : g));
@@ -269,6 +273,11 @@ extern "C" int pk_gemm_strided(const void* A, const void* B, void* C, const floa
                launch(gemm_strided_rows_kernel<bf16>, gr, br, sm, st, true, (const bf16*)A, (const bf16*)B, (bf16*)C, row_scale, cols, K, lda, sbn, ldc,
                       bsA, bsB, bsC, ld_scale, scale_kind));
     return (int)cudaGetLastError();
+  }
+  if (!f32 && sbk == 1 && rows >= 32) {  // many rows in bf16: the tensor-core kernel when the operands are laid out for it
+    const int rc = launch_gemm_batched_mma((const bf16*)A, (const bf16*)B, (bf16*)C, row_scale, rows, cols, K, lda, sbn, ldc, batch, bsA, bsB, bsC,
+                                           ld_scale, scale_kind, st);
+    if (rc != -2) return rc;
   }
   const dim3 g((cols + 63) / 64, (rows + 63) / 64, batch), b(256);
   PK_BY_TYPE(f32,

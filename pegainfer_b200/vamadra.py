@@ -222,6 +222,8 @@ def _typed_host():
     h.pv_request_pages.argtypes = [vp, i32, vp, i32]
     h.pv_step.argtypes = [vp, i32, vp, vp, vp, i32, vp, i32, vp, vp]
     h.pv_keep_trail.argtypes = [vp, i32]
+    h.pv_use_graph.argtypes = [vp, i32]
+    h.pv_graph_count.argtypes = [vp]
     h.pv_copy_trail.argtypes = [vp, vp]
     h.pv_launch_count.restype = C.c_int64
     h.pv_launch_count.argtypes = [vp, i32]
@@ -367,6 +369,13 @@ class VamadraModel:
         out = torch.empty((len(self.cfg.layers), tokens, self.cfg.width), dtype=torch.float32)
         self._ck(self._h.pv_copy_trail(self._m, out.data_ptr()))
         return out
+
+    def use_graph(self, on: bool = True) -> None:
+        """Decode steps (one token per entry) replay a captured launch sequence from their second occurrence on; off = always eager."""
+        self._h.pv_use_graph(self._m, int(on))
+
+    def graph_count(self) -> int:
+        return int(self._h.pv_graph_count(self._m))
 
     def launch_count(self, reset: bool = False) -> int:
         return int(self._h.pv_launch_count(self._m, int(reset)))

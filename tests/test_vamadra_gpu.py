@@ -501,6 +501,22 @@ def test_gemm_strided_is_exact_fp32_and_batches_heads(lib):
     assert torch.allclose(out.cpu(), want, atol=1e-5, rtol=1e-5)
 
 
+@pytest.mark.parametrize("T,H,r,v", [(150, 3, 40, 24), (70, 5, 64, 130), (33, 2, 36, 10)])
+def test_gemm_strided_bf16_many_rows(lib, T, H, r, v):
+    """per-head products over a prompt portion in bf16: the tensor-core kernel when the contraction length is a multiple of 8
+    (first two shapes), the plain kernel otherwise; ragged edges in every dimension"""
+    P = Hold()
+    g = torch.Generator().manual_seed(T)
+    A, B, s = (torch.randn(T, H, r, generator=g).to(BF16).to(F32), (torch.randn(H, v, r, generator=g) / math.sqrt(r)).to(BF16).to(F32),
+               torch.randn(T, H, generator=g))
+    out = torch.zeros(T, H, v, dtype=BF16, device="cuda")
+    assert lib.pk_gemm_strided(P(dev(A, BF16)), P(dev(B, BF16)), out.data_ptr(), P(s.cuda()), T, v, r, H * r, 1, r, H * v, H, r, v * r, v, H, 2, 0,
+                               None) == 0
+    torch.cuda.synchronize()
+    want = torch.einsum("thr,hvr->thv", A, B) * torch.sigmoid(s)[..., None]
+    assert torch.allclose(out.float().cpu(), want, atol=2e-2, rtol=2e-2)
+
+
 # ------------------------------------------------------------------ the model through its own entry points
 CASES = {"general": (cfg_general, 11), "edges": (cfg_edges, 12), "tiles": (cfg_tensor_tiles, 14)}
 
@@ -654,6 +670,30 @@ def test_far_key_in_a_long_prompt_and_long_decoding(oracle_cache):
     dec = torch.cat([m.step([(rid, [t])]) for t in toks[600:]])
     assert close(dec, want[600:], F32)
     m.close()
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_captured_decode_steps_equal_eager_ones(dtype, oracle_cache):
+    """single-token steps replay a captured launch sequence from their second occurrence; the context grows across the boundary of
+    a capture bucket (512), and two requests of unequal length decode side by side"""
+    cfg, w = cfg_tensor_tiles(), make_weights(cfg_tensor_tiles(), 14, sharp=SHARP[dtype])
+    ta, tb = tokens_for(cfg, 530, 41), tokens_for(cfg, 40, 42)
+    outs = {}
+    for graphs in (True, False):
+        m = build(cfg, w, dtype, max_tokens=640)
+        m.use_graph(graphs)
+        a, b = m.alloc_request(), m.alloc_request()
+        m.step([(a, ta[:500]), (b, tb[:10])])
+        rows = [m.step([(a, [ta[500 + i]]), (b, [tb[10 + i]])], [[0], [0]]) for i in range(30)]
+        outs[graphs] = torch.stack(rows)  # [30, 2, vocab]
+        assert (m.graph_count() >= 2) if graphs else (m.graph_count() == 0)
+        m.close()
+    assert close(outs[True].reshape(60, -1), outs[False].reshape(60, -1), dtype)
+    want_b = oracle_logits(oracle_cache, ("tiles", SHARP[dtype]), cfg, w, tb)
+    assert close(outs[True][:, 1], want_b[10:40], dtype)
+    if dtype == F32:
+        want_a = O.forward(cfg, w, ta)
+        assert close(outs[True][:, 0], want_a[500:530], dtype)
 
 
 def greedy_oracle(cfg, w, prompt, n):
