@@ -16,6 +16,7 @@ __global__ void __launch_bounds__(128) gemm_batched_mma_kernel(const bf16* __res
   __shared__ __align__(16) bf16 As[2][kBT * kBLd];
   __shared__ __align__(16) bf16 Bs[2][kBT * kBLd];
   pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   const int bz = blockIdx.z, m0 = blockIdx.y * kBT, n0 = blockIdx.x * kBT;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tq = lane & 3, wm = warp >> 1, wn = warp & 1;
   A += (size_t)bz * bsA;

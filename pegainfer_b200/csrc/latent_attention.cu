@@ -24,6 +24,7 @@ template <typename E>
 __global__ void rope_slice_kernel(const E* __restrict__ in, E* __restrict__ out, const int* __restrict__ pos, const float* __restrict__ freq,
                                   float mag, int heads, int in_stride, int in_off, int out_stride, int out_off, int width, int dims) {
   pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   const int t = blockIdx.x, half = dims / 2;
   const float p = (float)pos[t];
   for (int e = threadIdx.x; e < heads * width; e += blockDim.x) {
@@ -51,6 +52,7 @@ __global__ void latent_kv_append_kernel(const E* __restrict__ dkv, const E* __re
                                         const float* __restrict__ freq, float mag, float eps) {
   __shared__ float red[33];
   pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   const int t = blockIdx.x, p = pos[t], half = dims / 2;
   const E* d = dkv + (size_t)t * (rank + rot);
   E* dst = cache + (size_t)pages[page_off[req[t]] + p / page_size] * page_stride + (size_t)(p % page_size) * (rank + rot);
@@ -89,6 +91,7 @@ __global__ void latent_attention_kernel(const E* __restrict__ qa, const E* __res
                                         int rank, int rot, float scale) {
   extern __shared__ float sm[];
   pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   const int t = blockIdx.x, h = blockIdx.y, D = rank + rot;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   float* q_s = sm;                 // [D]

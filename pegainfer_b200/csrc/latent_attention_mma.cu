@@ -40,6 +40,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, const bf16* __restrict_
   const int total_rows = tokens * heads, R0 = blockIdx.x * ROWS;
   const int split = blockIdx.y, nsplit = gridDim.y;
   pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
 
   // ---- Q tile (rows past the end are zero)
   const int chunks = D / 8;  // 16-byte pieces per row
@@ -261,6 +262,7 @@ __global__ void latent_attention_merge_kernel(const float* __restrict__ part_o, 
                                               bf16* __restrict__ out, int nsplit, int heads, int rank, int tile_rows) {
   __shared__ float wgt[64];  // per split: exp(m_s - M) / denominator
   pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   const int R = blockIdx.x, tile = R / tile_rows, r = R % tile_rows;
   const size_t slot0 = (size_t)tile * nsplit * tile_rows + r;  // split s at slot0 + s * tile_rows
   if (threadIdx.x < 32) {
@@ -319,7 +321,7 @@ int launch_latent_attention_mma(const bf16* qa, const bf16* cache, const bf16* s
   int splits = 1;
   ThreadState& ts = tls();
   if (max_kv_len > 2 * kMmaKeys && tiles < 2 * sm_count() && ts.scratch) {
-    splits = min(min((2 * sm_count() + tiles - 1) / tiles, (max_kv_len + 2 * kMmaKeys - 1) / (2 * kMmaKeys)), 64);
+    splits = min(min((2 * sm_count() + tiles - 1) / tiles, (max_kv_len + kMmaKeys - 1) / kMmaKeys), 64);
     while (splits > 1 && (size_t)tiles * splits * rows * (rank + 2) * 4 > ts.scratch_bytes) --splits;
   }
   float* po = static_cast<float*>(ts.scratch);

@@ -29,6 +29,7 @@ __global__ void router_grouped_topk_kernel(const float* __restrict__ z, int* __r
                                            int groups, int keep, float scale) {
   extern __shared__ float sm[];
   pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   const int t = blockIdx.x, lane = threadIdx.x;
   float* s = sm;            // [E]
   float* gs = s + E;        // [groups] group score, -1 once taken
@@ -101,6 +102,7 @@ __global__ void moe_up_kernel(const E* __restrict__ xa, const E* __restrict__ w_
                               int ff) {
   extern __shared__ __align__(16) float xs[];
   pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int tok = blockIdx.x, k = blockIdx.y, top = gridDim.y;
   for (int i = threadIdx.x; i < width; i += blockDim.x) xs[i] = to_f(xa[(size_t)tok * width + i]);
@@ -122,6 +124,7 @@ __global__ void moe_down_kernel(const E* __restrict__ hid, const E* __restrict__
                                 const E* __restrict__ shared, const float* __restrict__ sg, float* __restrict__ y, int width, int ff, int top) {
   extern __shared__ __align__(16) float hs[];  // [top][ffp], ffp = ff rounded up to 4 so that every row starts 16-byte aligned
   pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int ffp = (ff + 3) & ~3;
   for (int i = threadIdx.x; i < top * ff; i += blockDim.x) hs[(i / ff) * ffp + i % ff] = to_f(hid[(size_t)t * top * ff + i]);

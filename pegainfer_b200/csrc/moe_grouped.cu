@@ -22,6 +22,7 @@ __global__ void moe_bucket_kernel(const int* __restrict__ ids, int pairs, int ex
                                   int* __restrict__ slot_pair, int* __restrict__ pair_slot) {
   extern __shared__ int sh[];  // [experts] counts, then [experts] cursors
   pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   int* cnt = sh;
   int* cur = sh + experts;
   for (int e = threadIdx.x; e < experts; e += blockDim.x) cnt[e] = 0;
@@ -64,6 +65,7 @@ __global__ void __launch_bounds__(128) moe_grouped_gemm_kernel(const bf16* __res
   __shared__ __align__(16) bf16 As[2][kGT * kGLd];
   __shared__ __align__(16) bf16 Bs[2][kGT * kGLd];
   pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   if ((int)blockIdx.y >= meta[0]) return;
   const int* off = meta + 1;
   const int e = meta[2 + experts + blockIdx.y], m0 = meta[2 + experts + max_tiles + blockIdx.y];
@@ -146,6 +148,7 @@ __global__ void __launch_bounds__(128) moe_grouped_gemm_kernel(const bf16* __res
 __global__ void moe_combine_kernel(const float* __restrict__ part, const int* __restrict__ pair_slot, const bf16* __restrict__ shared,
                                    const float* __restrict__ sg, float* __restrict__ y, int width, int top) {
   pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   const int t = blockIdx.x;
   const float g = shared ? 1.f / (1.f + expf(-sg[t])) : 0.f;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {

@@ -14,6 +14,7 @@ template <typename E>
 __global__ void embed_res32_kernel(const E* __restrict__ embed, const int* __restrict__ tok, float* __restrict__ x,
                                    E* __restrict__ xa, int width) {
   pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   const int t = blockIdx.x;
   const E* row = embed + (size_t)tok[t] * width;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
@@ -29,6 +30,7 @@ __global__ void offset_norm_residual_kernel(const Y* __restrict__ y, const E* __
                                             E* __restrict__ xa, int width, float eps) {
   __shared__ float red[33];
   pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   const int t = blockIdx.x;
   const Y* yr = y + (size_t)t * width;
   float ss = 0.f;
@@ -51,6 +53,7 @@ __global__ void offset_norm_rows_kernel(const float* __restrict__ x, const int* 
                                         E* __restrict__ out, int width, float eps) {
   __shared__ float red[33];
   pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   const float* xr = x + (size_t)rows[blockIdx.x] * width;
   float ss = 0.f;
   for (int i = threadIdx.x; i < width; i += blockDim.x) ss += xr[i] * xr[i];
@@ -64,6 +67,7 @@ __global__ void offset_norm_rows_kernel(const float* __restrict__ x, const int* 
 template <typename E>
 __global__ void skinny_proj_kernel(const E* __restrict__ W, const float* __restrict__ x, float* __restrict__ out, int M, int K) {
   pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const float* xr = x + (size_t)t * K;
   for (int m = blockIdx.y * nw + warp; m < M; m += gridDim.y * nw) {
@@ -77,6 +81,7 @@ __global__ void skinny_proj_kernel(const E* __restrict__ W, const float* __restr
 template <typename E>
 __global__ void act_kernel(const E* __restrict__ in, E* __restrict__ out, int F, long total, int kind) {
   pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
     const long t = i / F, f = i % F;
     float r;
@@ -94,6 +99,7 @@ __global__ void act_kernel(const E* __restrict__ in, E* __restrict__ out, int F,
 template <typename A, typename B>
 __global__ void convert_kernel(const A* __restrict__ in, B* __restrict__ out, long n) {
   pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) out[i] = from_f<B>(to_f(in[i]));
 }
 
@@ -106,6 +112,7 @@ __global__ void gemm_strided_kernel(const E* __restrict__ A, const E* __restrict
   constexpr int TL = 64, KT = 16;
   __shared__ float as[KT][TL + 1], bs[KT][TL + 1];
   pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   const int b = blockIdx.z;
   A += (size_t)b * bsA;
   B += (size_t)b * bsB;
@@ -169,6 +176,7 @@ __global__ void gemm_strided_rows_kernel(const E* __restrict__ A, const E* __res
                                          int cols, int K, long lda, long sbn, long ldc, long bsA, long bsB, long bsC, int ld_scale, int scale_kind) {
   extern __shared__ __align__(16) float a_s[];
   pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   const int i = blockIdx.x, b = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const E* a = A + (size_t)b * bsA + (size_t)i * lda;
   for (int k = threadIdx.x; k < K; k += blockDim.x) a_s[k] = to_f(a[k]);
