@@ -420,6 +420,9 @@ int pk_res32_offset_norm_add(const void* y, int y_is_f32, const void* w, float* 
 int pk_res32_offset_norm_rows(const float* x, const int* rows, const void* w, void* out, int width, int n_rows, float eps, int f32, pk_stream st);
 /* out[t][m] = W[m] . x[t] with fp32 input, accumulation and output (router logits, gates): M small */
 int pk_res32_skinny_proj(const void* W, const float* x, float* out, int M, int K, int tokens, int f32, pk_stream st);
+/* the same projection for many tokens from the bf16 copy of the residual, on the tensor cores, fp32 accumulation and output;
+ * -2: K not a multiple of 8 or misaligned */
+int pk_proj_rows_f32out(const void* W, const void* xa, float* out, int M, int K, int tokens, pk_stream st);
 /* kind 0: out[t][f] = silu(in[t][f]) * in[t][F + f] (in [tokens, 2F]);  kind 1: out[t][f] = relu(in[t][f])^2 (in [tokens, F]) */
 int pk_act(const void* in, void* out, int F, int tokens, int kind, int f32, pk_stream st);
 int pk_convert(const void* in, int in_f32, void* out, int out_f32, long n, pk_stream st);

@@ -10,7 +10,8 @@ namespace pk {
 
 constexpr int kBT = 64, kBK = 32, kBLd = kBK + 8;
 
-__global__ void __launch_bounds__(128) gemm_batched_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, bf16* __restrict__ C,
+template <typename OUT>  // bf16, or float for products whose result must stay fp32 (router logits, gates)
+__global__ void __launch_bounds__(128) gemm_batched_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, OUT* __restrict__ C,
                                                               const float* __restrict__ row_scale, int rows, int cols, int K, long lda, long ldb,
                                                               long ldc, long bsA, long bsB, long bsC, int ld_scale, int scale_kind) {
   __shared__ __align__(16) bf16 As[2][kBT * kBLd];
@@ -81,12 +82,17 @@ __global__ void __launch_bounds__(128) gemm_batched_mma_kernel(const bf16* __res
 #pragma unroll
       for (int ni = 0; ni < 4; ++ni) {
         const int j = n0 + wn * 32 + ni * 8 + 2 * tq;
-        bf16* o = C + (size_t)i * ldc + j;
+        OUT* o = C + (size_t)i * ldc + j;
         const float v0 = acc[mi][ni][hf * 2] * s, v1 = acc[mi][ni][hf * 2 + 1] * s;
-        if (j + 1 < cols && (reinterpret_cast<uintptr_t>(o) & 3) == 0) *reinterpret_cast<uint32_t*>(o) = pack_bf16(v0, v1);
-        else {
-          if (j < cols) o[0] = f2bf(v0);
-          if (j + 1 < cols) o[1] = f2bf(v1);
+        if constexpr (sizeof(OUT) == 4) {
+          if (j < cols) o[0] = v0;
+          if (j + 1 < cols) o[1] = v1;
+        } else {
+          if (j + 1 < cols && (reinterpret_cast<uintptr_t>(o) & 3) == 0) *reinterpret_cast<uint32_t*>(o) = pack_bf16(v0, v1);
+          else {
+            if (j < cols) o[0] = f2bf(v0);
+            if (j + 1 < cols) o[1] = f2bf(v1);
+          }
         }
       }
     }
@@ -96,9 +102,19 @@ __global__ void __launch_bounds__(128) gemm_batched_mma_kernel(const bf16* __res
 int launch_gemm_batched_mma(const bf16* A, const bf16* B, bf16* C, const float* row_scale, int rows, int cols, int K, long lda, long ldb, long ldc,
                             int batch, long bsA, long bsB, long bsC, int ld_scale, int scale_kind, cudaStream_t st) {
   if (K % 8 || lda % 8 || ldb % 8 || bsA % 8 || bsB % 8 || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -2;
-  const cudaError_t e = launch(gemm_batched_mma_kernel, dim3((cols + kBT - 1) / kBT, (rows + kBT - 1) / kBT, batch), dim3(128), 0, st, true, A, B, C,
-                               row_scale, rows, cols, K, lda, ldb, ldc, bsA, bsB, bsC, ld_scale, scale_kind);
+  const cudaError_t e = launch(gemm_batched_mma_kernel<bf16>, dim3((cols + kBT - 1) / kBT, (rows + kBT - 1) / kBT, batch), dim3(128), 0, st, true, A, B,
+                               C, row_scale, rows, cols, K, lda, ldb, ldc, bsA, bsB, bsC, ld_scale, scale_kind);
   return (int)e;
 }
 
 }  // namespace pk
+
+// out[t][m] (fp32) = W[m] . xa[t] with bf16 operands and fp32 accumulation: the skinny projections (router logits, gates) of a
+// prompt portion on the tensor cores.  -2: K not a multiple of 8 or misaligned (the caller runs pk_res32_skinny_proj).
+extern "C" int pk_proj_rows_f32out(const void* W, const void* xa, float* out, int M, int K, int tokens, pk_stream st) {
+  using namespace pk;
+  if (!W || !xa || !out || M <= 0 || K <= 0 || tokens <= 0) return -1;
+  if (K % 8 || (reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(xa) & 15)) return -2;
+  return (int)launch(gemm_batched_mma_kernel<float>, dim3((M + kBT - 1) / kBT, (tokens + kBT - 1) / kBT, 1), dim3(128), 0, st, true, (const bf16*)xa,
+                     (const bf16*)W, out, (const float*)nullptr, tokens, M, K, (long)K, (long)K, (long)M, 0L, 0L, 0L, 0, 0);
+}

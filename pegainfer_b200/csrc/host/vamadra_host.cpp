@@ -54,7 +54,7 @@ struct Lib {
   PV_FN(pk_b200_launch_count) PV_FN(pk_res32_embed) PV_FN(pk_res32_offset_norm_add) PV_FN(pk_res32_offset_norm_rows)
   PV_FN(pk_res32_skinny_proj) PV_FN(pk_act) PV_FN(pk_convert) PV_FN(pk_gemm_strided) PV_FN(pk_rope_slice) PV_FN(pk_latent_kv_append)
   PV_FN(pk_latent_attention) PV_FN(pk_router_grouped_topk) PV_FN(pk_moe_up_relu2) PV_FN(pk_moe_down_combine)
-  PV_FN(pk_moe_grouped_workspace_bytes) PV_FN(pk_moe_grouped_relu2)
+  PV_FN(pk_moe_grouped_workspace_bytes) PV_FN(pk_moe_grouped_relu2) PV_FN(pk_proj_rows_f32out)
 #undef PV_FN
   std::string load(const std::string& p) {
     handle = dlopen(p.c_str(), RTLD_NOW | RTLD_LOCAL);
@@ -67,7 +67,7 @@ struct Lib {
     PV_REQ(pk_b200_launch_count) PV_REQ(pk_res32_embed) PV_REQ(pk_res32_offset_norm_add) PV_REQ(pk_res32_offset_norm_rows)
     PV_REQ(pk_res32_skinny_proj) PV_REQ(pk_act) PV_REQ(pk_convert) PV_REQ(pk_gemm_strided) PV_REQ(pk_rope_slice) PV_REQ(pk_latent_kv_append)
     PV_REQ(pk_latent_attention) PV_REQ(pk_router_grouped_topk) PV_REQ(pk_moe_up_relu2) PV_REQ(pk_moe_down_combine)
-    PV_REQ(pk_moe_grouped_workspace_bytes) PV_REQ(pk_moe_grouped_relu2)
+    PV_REQ(pk_moe_grouped_workspace_bytes) PV_REQ(pk_moe_grouped_relu2) PV_REQ(pk_proj_rows_f32out)
 #undef PV_REQ
     return missing.empty() ? "" : "kernel library " + p + " lacks:" + missing;
   }
@@ -154,6 +154,7 @@ struct Model {
   bool finalize();
   bool ensure_scratch(int T, int R);
   bool lin(const Mat& W, const void* X, void* Y, int N);
+  bool skinny(const Mat& W, float* out, int T, const char* what);
   bool run_layer(int li, int T, int max_kv, const int* d_pos, const int* d_req, const int* d_poff, const int* d_pages);
   bool forward(int T, int n, int n_rows, int max_kv, int want_sample);
   bool step(int n, const int* tokens, const int* lens, const int* rids, int n_rows, const int* rows, int want_sample);
@@ -398,6 +399,16 @@ bool Model::lin(const Mat& W, const void* X, void* Y, int N) {
   return true;
 }
 
+// out[T, W.rows] (fp32) = residual W^T for the few-row projections (gates, router): from the fp32 residual per token, or -- for
+// a prompt portion in bf16 -- from its bf16 copy on the tensor cores (fp32 accumulation and output either way)
+bool Model::skinny(const Mat& W, float* out, int T, const char* what) {
+  if (!c.f32 && T >= kGroupedMinTokens) {
+    const int r = k.pk_proj_rows_f32out(W.d.ptr, xa.ptr, out, W.rows, W.cols, T, st);
+    if (r != -2) return rc(r, what);
+  }
+  return rc(k.pk_res32_skinny_proj(W.d.ptr, (const float*)x.ptr, out, W.rows, W.cols, T, c.f32, st), what);
+}
+
 bool Model::run_layer(int li, int T, int max_kv, const int* d_pos, const int* d_req, const int* d_poff, const int* d_pages) {
   Layer& L = layers[li];
   const LayerCfg& a = L.c;
@@ -420,7 +431,7 @@ bool Model::run_layer(int li, int T, int max_kv, const int* d_pos, const int* d_
   if (rd > 0 && !rc(k.pk_rope_slice(q.ptr, qa.ptr, d_pos, (const float*)L.freq.ptr, L.mag, T, H, a.dim + rd, a.dim, D, r, rd, a.rot_dims, f32, st),
                     "query rotation"))
     return false;
-  if (!rc(k.pk_res32_skinny_proj(L.g.d.ptr, (const float*)x.ptr, (float*)gate.ptr, H, W, T, f32, st), "output gate")) return false;
+  if (!skinny(L.g, (float*)gate.ptr, T, "output gate")) return false;
   if (!rc(k.pk_latent_attention(qa.ptr, pool_base, L.sink.d.ptr, d_pos, d_req, d_poff, d_pages, olat.ptr, page_stride, c.page_size, T, H, r, rd,
                                 a.scale, max_kv, f32, st),
           "latent attention"))
@@ -439,7 +450,7 @@ bool Model::run_layer(int li, int T, int max_kv, const int* d_pos, const int* d_
     if (!lin(L.down, act.ptr, mix.ptr, T)) return false;
     if (!rc(k.pk_res32_offset_norm_add(mix.ptr, f32, L.norm2.d.ptr, (float*)x.ptr, xa.ptr, W, T, c.eps, f32, st), "norm2")) return false;
   } else if (a.mlp_kind == 2) {
-    if (!rc(k.pk_res32_skinny_proj(L.router.d.ptr, (const float*)x.ptr, (float*)z.ptr, a.experts, W, T, f32, st), "router")) return false;
+    if (!skinny(L.router, (float*)z.ptr, T, "router")) return false;
     if (!rc(k.pk_router_grouped_topk((const float*)z.ptr, (int*)ids.ptr, (float*)wts.ptr, T, a.experts, a.top, a.groups, a.keep, a.route_scale, st),
             "router top-k"))
       return false;
@@ -448,7 +459,7 @@ bool Model::run_layer(int li, int T, int max_kv, const int* d_pos, const int* d_
       if (!lin(L.s_up, xa.ptr, gu.ptr, T)) return false;
       if (!rc(k.pk_act(gu.ptr, act.ptr, a.shared_ff, T, 1, f32, st), "shared expert activation")) return false;
       if (!lin(L.s_down, act.ptr, sh.ptr, T)) return false;
-      if (!rc(k.pk_res32_skinny_proj(L.s_gate.d.ptr, (const float*)x.ptr, (float*)sgl.ptr, 1, W, T, f32, st), "shared expert gate")) return false;
+      if (!skinny(L.s_gate, (float*)sgl.ptr, T, "shared expert gate")) return false;
       shared = sh.ptr;
     }
     // many tokens: rows bucketed by expert on the tensor cores; a few tokens: per token, reading only the chosen experts' weights

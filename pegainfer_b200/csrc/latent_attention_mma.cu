@@ -281,10 +281,19 @@ __global__ void latent_attention_merge_kernel(const float* __restrict__ part_o, 
     wgt[threadIdx.x + 32] = e1 * inv;
   }
   __syncthreads();
-  for (int d = threadIdx.x; d < rank; d += blockDim.x) {
-    float acc = 0.f;
-    for (int s = 0; s < nsplit; ++s) acc = fmaf(part_o[(slot0 + (size_t)s * tile_rows) * rank + d], wgt[s], acc);
-    out[(size_t)R * rank + d] = f2bf(acc);
+  const int d = blockIdx.y * blockDim.x + threadIdx.x;  // one output column per thread; the splits' loads are independent
+  if (d < rank) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    int s = 0;
+    for (; s + 4 <= nsplit; s += 4) {
+      float v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = part_o[(slot0 + (size_t)(s + u) * tile_rows) * rank + d];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) acc[u] = fmaf(v[u], wgt[s + u], acc[u]);
+    }
+    for (; s < nsplit; ++s) acc[0] = fmaf(part_o[(slot0 + (size_t)s * tile_rows) * rank + d], wgt[s], acc[0]);
+    out[(size_t)R * rank + d] = f2bf((acc[0] + acc[1]) + (acc[2] + acc[3]));
   }
 }
 
@@ -345,7 +354,7 @@ int launch_latent_attention_mma(const bf16* qa, const bf16* cache, const bf16* s
 #undef PK_LAUNCH_MMA
   if (e != cudaSuccess) return (int)e;
   if (splits > 1)
-    e = launch(latent_attention_merge_kernel, dim3(total), dim3(128), 0, st, true, (const float*)po, (const float*)pml, sink, out, splits, heads, rank,
+    e = launch(latent_attention_merge_kernel, dim3(total, (rank + 127) / 128), dim3(128), 0, st, true, (const float*)po, (const float*)pml, sink, out, splits, heads, rank,
                rows);
   return (int)e;
 }

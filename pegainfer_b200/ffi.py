@@ -114,6 +114,7 @@ RES32_SIGNATURES = {
     "pk_res32_offset_norm_add": (i32, [vp, i32, vp, vp, vp, i32, i32, f32, i32, vp]),
     "pk_res32_offset_norm_rows": (i32, [vp, vp, vp, vp, i32, i32, f32, i32, vp]),
     "pk_res32_skinny_proj": (i32, [vp, vp, vp, i32, i32, i32, i32, vp]),
+    "pk_proj_rows_f32out": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "pk_act": (i32, [vp, vp, i32, i32, i32, i32, vp]),
     "pk_convert": (i32, [vp, i32, vp, i32, i64l, vp]),
     "pk_gemm_strided": (i32, [vp, vp, vp, vp, i32, i32, i32, i64l, i64l, i64l, i64l, i32, i64l, i64l, i64l, i32, i32, i32, vp]),

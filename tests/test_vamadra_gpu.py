@@ -517,6 +517,20 @@ def test_gemm_strided_bf16_many_rows(lib, T, H, r, v):
     assert torch.allclose(out.float().cpu(), want, atol=2e-2, rtol=2e-2)
 
 
+def test_few_row_projection_of_a_prompt_portion_keeps_fp32_results(lib):
+    """router logits / gates of many tokens: bf16 operands on the tensor cores, fp32 accumulation and fp32 output"""
+    P = Hold()
+    g = torch.Generator().manual_seed(21)
+    T, M, K = 100, 12, 72
+    x, W = torch.randn(T, K, generator=g).to(BF16).to(F32), (4 * torch.randn(M, K, generator=g)).to(BF16).to(F32)
+    out = torch.zeros(T, M, device="cuda")
+    assert lib.pk_proj_rows_f32out(P(dev(W, BF16)), P(dev(x, BF16)), out.data_ptr(), M, K, T, None) == 0
+    torch.cuda.synchronize()
+    want = x.double() @ W.double().T
+    assert (out.cpu().double() - want).abs().max() < 2e-5 * want.abs().max()  # exact products of bf16 values, fp32 sums: no bf16 rounding of the result
+    assert lib.pk_proj_rows_f32out(P(dev(W[:, :70], BF16)), P(dev(x[:, :70], BF16)), out.data_ptr(), M, 70, T, None) == -2  # 70 % 8 != 0: not for this kernel
+
+
 # ------------------------------------------------------------------ the model through its own entry points
 CASES = {"general": (cfg_general, 11), "edges": (cfg_edges, 12), "tiles": (cfg_tensor_tiles, 14)}
 
