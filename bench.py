@@ -817,10 +817,13 @@ def run_arch_compare(args):
         for bs in (1, 4):
             rids = [vm.alloc_request() for _ in range(bs)]
             vm.step([(r, synthetic_prompt(ctx, i)) for i, r in enumerate(rids)])
+            vm.use_graph(False)  # one eager step to count the kernels a step launches (replayed graphs bypass the counter)
             vm.launch_count(True)
+            vm.step([(r, [7]) for r in rids], sample=True)
+            res[f"decode_bs{bs}_launches_per_step"] = vm.launch_count()
+            vm.use_graph(True)
             t = med(lambda: vm.step([(r, [7]) for r in rids], sample=True))
             res[f"decode_bs{bs}_ctx{ctx}_tok_s"] = round(bs / t, 1)
-            res[f"decode_bs{bs}_launches_per_step"] = vm.launch_count() // (warm + reps)
             for r in rids:
                 vm.drop_request(r)
         row["vamadra"] = res

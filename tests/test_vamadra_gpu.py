@@ -566,8 +566,9 @@ def test_whole_prompt_every_position_and_every_layer(case, dtype, oracle_cache):
     assert close(got, want, dtype)
     # the very first tokens of a sequence, alone: positions 0 and 1
     r2 = m.alloc_request()
-    assert close(m.step([(r2, toks[:1])]), want[:1], dtype)
-    assert close(m.step([(r2, toks[1:2])]), want[1:2], dtype)
+    one = 2e-4 if dtype == F32 else 0.15  # a single row: no percentiles to take
+    assert row_errors(m.step([(r2, toks[:1])]), want[:1]).item() < one
+    assert row_errors(m.step([(r2, toks[1:2])]), want[1:2]).item() < one
     m.close()
 
 
