@@ -182,7 +182,7 @@ bool Model::configure(const ModelCfg& mc, const LayerCfg* lc) {
     const LayerCfg& a = L.c;
     if (a.heads <= 0 || a.dim <= 0 || a.vdim <= 0 || a.kv_rank <= 0 || a.rot_dim < 0) return fail(lname(i, "mixer: sizes must be positive"));
     if (a.rot_dims < 0 || a.rot_dims > a.rot_dim || (a.rot_dims & 1)) return fail(lname(i, "mixer: rot.dims must be even and at most rot_dim"));
-    if (a.kv_rank > 512) return fail(lname(i, "mixer: kv_rank above 512 is outside the attention kernel's range"));
+    if (a.kv_rank > 1024) return fail(lname(i, "mixer: kv_rank above 1024 is outside the attention kernel's range"));
     if (a.kv_from >= 0) {
       if (a.kv_from >= i || layers[a.kv_from].c.kv_from >= 0) return fail(lname(i, "mixer: kv_from must name an earlier layer that owns a cache"));
       const LayerCfg& o = layers[a.kv_from].c;
@@ -196,7 +196,7 @@ bool Model::configure(const ModelCfg& mc, const LayerCfg* lc) {
     }
     if (a.mlp_kind == 1 && a.ff <= 0) return fail(lname(i, "mlp: ff must be positive"));
     if (a.mlp_kind == 2) {
-      if (a.experts <= 0 || a.top <= 0 || a.top > 32 || a.expert_ff <= 0 || a.groups <= 0 || a.experts % a.groups || a.keep <= 0 || a.keep > a.groups ||
+      if (a.experts <= 0 || a.top <= 0 || a.expert_ff <= 0 || a.groups <= 0 || a.experts % a.groups || a.keep <= 0 || a.keep > a.groups ||
           a.top > a.keep * (a.experts / a.groups))
         return fail(lname(i, "mlp: inconsistent router (experts, top, groups)"));
     }

@@ -80,7 +80,7 @@ __global__ void latent_kv_append_kernel(const E* __restrict__ dkv, const E* __re
   }
 }
 
-constexpr int kLatentMaxPerLane = 16;  // rank <= 512
+constexpr int kLatentMaxPerLane = 32;  // rank <= 1024
 
 // Generic-width kernel: one block per (query row, head); warps stride over the visible keys with an online softmax each,
 // lanes split the feature axis; the per-warp states and the sink are merged at the end.

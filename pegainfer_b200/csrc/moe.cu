@@ -90,7 +90,7 @@ __global__ void router_grouped_topk_kernel(const float* __restrict__ z, int* __r
     }
     __syncwarp();
   }
-  if (lane < top) wts[(size_t)t * top + lane] = wts[(size_t)t * top + lane] / (total + 1e-20f) * scale;
+  for (int r = lane; r < top; r += 32) wts[(size_t)t * top + r] = wts[(size_t)t * top + r] / (total + 1e-20f) * scale;
 }
 
 constexpr int kMoeDownRowsPerBlock = 8;  // one output row per warp: each row already streams `top` weight rows
@@ -147,7 +147,7 @@ using namespace pk;
 
 extern "C" int pk_router_grouped_topk(const float* logits, int* ids, float* weights, int tokens, int experts, int top, int groups, int keep,
                                       float scale, pk_stream st) {
-  if (!logits || !ids || !weights || tokens <= 0 || experts <= 0 || top <= 0 || top > 32 || groups <= 0 || experts % groups || keep <= 0 ||
+  if (!logits || !ids || !weights || tokens <= 0 || experts <= 0 || top <= 0 || groups <= 0 || experts % groups || keep <= 0 ||
       keep > groups || top > keep * (experts / groups))
     return -1;
   launch(router_grouped_topk_kernel, dim3(tokens), dim3(32), (size_t)(experts + 2 * groups) * sizeof(float), st, true, logits, ids, weights, experts,

@@ -23,9 +23,14 @@ class Engine:
         for name, tokens, w in entries:
             if name not in self.slots:
                 self.slots[name] = self.model.alloc_request()
+            if len(tokens) == 0:  # admitted, nothing to run for it in this step
+                continue
             batch.append((self.slots[name], tokens))
             want.append(list(w))
         try:
+            if not batch:
+                import torch
+                return torch.empty((0, 0), dtype=torch.float32)
             return self.model.step(batch, want)
         finally:
             for name in end:

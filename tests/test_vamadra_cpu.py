@@ -112,6 +112,9 @@ def test_engine_explicit_steps_admit_and_release():
     assert "x" not in e.slots and m.len == {e.slots["y"]: 1}
     e.step([("z", [1], [0]), ("y", [2], [0])], end=["y", "z"])             # z reuses the slot x held
     assert not e.slots and sorted(m.free) == [0, 1]
+    assert e.step([("w", [], [])]).shape[0] == 0 and "w" in e.slots and len(m.steps) == 3  # admitted, nothing ran
+    assert e.step([("w", [], []), ("v", [3, 4], [1])]).shape[0] == 1                       # an empty entry beside a real one
+    e.release("w"), e.release("v")
 
 
 def test_trace_replay_writes_logits_and_done_lines(tmp_path, monkeypatch, capsys):

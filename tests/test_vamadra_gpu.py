@@ -261,7 +261,7 @@ def oracle_attention(qa, c, kr, sink, pos, scale):
 
 # (heads, rank, rot): the first runs the generic kernel; bf16 with rank % 64 == 0 and rot % 16 == 0 runs the tensor-core kernel, whose
 # 16-row tiles then hold several tokens' heads (3, 7), a token's heads exactly (16), or part of them (20)
-ATTN_SHAPES = [(3, 40, 12), (7, 64, 48), (3, 64, 16), (16, 128, 0), (20, 128, 16), (5, 256, 64)]
+ATTN_SHAPES = [(3, 40, 12), (7, 64, 48), (3, 64, 16), (16, 128, 0), (20, 128, 16), (5, 256, 64), (2, 544, 8)]
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
@@ -350,7 +350,7 @@ def test_latent_attention_single_keys_stand_out(lib):
         assert torch.allclose(got[0, h], wgt * c[0], atol=1e-5)
 
 
-@pytest.mark.parametrize("E,top,count,keep", [(10, 3, 5, 2), (8, 2, 1, 1), (6, 1, 3, 3), (16, 4, 8, 2), (5, 5, 1, 1)])
+@pytest.mark.parametrize("E,top,count,keep", [(10, 3, 5, 2), (8, 2, 1, 1), (6, 1, 3, 3), (16, 4, 8, 2), (5, 5, 1, 1), (40, 33, 2, 2)])
 def test_router_grouped_topk(lib, E, top, count, keep):
     P = Hold()
     T = 64
@@ -566,9 +566,11 @@ def test_whole_prompt_every_position_and_every_layer(case, dtype, oracle_cache):
     assert close(got, want, dtype)
     # the very first tokens of a sequence, alone: positions 0 and 1
     r2 = m.alloc_request()
-    one = 2e-4 if dtype == F32 else 0.15  # a single row: no percentiles to take
-    assert row_errors(m.step([(r2, toks[:1])]), want[:1]).item() < one
-    assert row_errors(m.step([(r2, toks[1:2])]), want[1:2]).item() < one
+    # (float32 against the oracle; bfloat16 against the same rows of the whole prompt above: one row has no percentiles, and a
+    # routing decision that rounding flips is flipped in both)
+    ref, one = (want, 2e-4) if dtype == F32 else (got, 0.05)
+    assert row_errors(m.step([(r2, toks[:1])]), ref[:1]).item() < one
+    assert row_errors(m.step([(r2, toks[1:2])]), ref[1:2]).item() < one
     m.close()
 
 
