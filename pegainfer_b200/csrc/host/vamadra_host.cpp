@@ -54,7 +54,7 @@ struct Lib {
   PV_FN(pk_b200_launch_count) PV_FN(pk_res32_embed) PV_FN(pk_res32_offset_norm_add) PV_FN(pk_res32_offset_norm_rows)
   PV_FN(pk_res32_skinny_proj) PV_FN(pk_act) PV_FN(pk_convert) PV_FN(pk_gemm_strided) PV_FN(pk_rope_slice) PV_FN(pk_latent_kv_append)
   PV_FN(pk_latent_attention) PV_FN(pk_router_grouped_topk) PV_FN(pk_moe_up_relu2) PV_FN(pk_moe_down_combine)
-  PV_FN(pk_moe_grouped_workspace_bytes) PV_FN(pk_moe_grouped_relu2) PV_FN(pk_proj_rows_f32out)
+  PV_FN(pk_moe_grouped_workspace_bytes) PV_FN(pk_moe_grouped_relu2) PV_FN(pk_proj_rows_f32out) PV_FN(pk_b200_gemv_fused) PV_FN(pk_b200_gemm_swiglu)
 #undef PV_FN
   std::string load(const std::string& p) {
     handle = dlopen(p.c_str(), RTLD_NOW | RTLD_LOCAL);
@@ -67,7 +67,7 @@ struct Lib {
     PV_REQ(pk_b200_launch_count) PV_REQ(pk_res32_embed) PV_REQ(pk_res32_offset_norm_add) PV_REQ(pk_res32_offset_norm_rows)
     PV_REQ(pk_res32_skinny_proj) PV_REQ(pk_act) PV_REQ(pk_convert) PV_REQ(pk_gemm_strided) PV_REQ(pk_rope_slice) PV_REQ(pk_latent_kv_append)
     PV_REQ(pk_latent_attention) PV_REQ(pk_router_grouped_topk) PV_REQ(pk_moe_up_relu2) PV_REQ(pk_moe_down_combine)
-    PV_REQ(pk_moe_grouped_workspace_bytes) PV_REQ(pk_moe_grouped_relu2) PV_REQ(pk_proj_rows_f32out)
+    PV_REQ(pk_moe_grouped_workspace_bytes) PV_REQ(pk_moe_grouped_relu2) PV_REQ(pk_proj_rows_f32out) PV_REQ(pk_b200_gemv_fused) PV_REQ(pk_b200_gemm_swiglu)
 #undef PV_REQ
     return missing.empty() ? "" : "kernel library " + p + " lacks:" + missing;
   }
@@ -445,8 +445,27 @@ bool Model::run_layer(int li, int T, int max_kv, const int* d_pos, const int* d_
   if (!rc(k.pk_res32_offset_norm_add(mix.ptr, f32, L.norm1.d.ptr, (float*)x.ptr, xa.ptr, W, T, c.eps, f32, st), "norm1")) return false;
   // ---- feed-forward
   if (a.mlp_kind == 1) {
-    if (!lin(L.gate_up, xa.ptr, gu.ptr, T)) return false;
-    if (!rc(k.pk_act(gu.ptr, act.ptr, a.ff, T, 0, f32, st), "SwiGLU")) return false;
+    // bf16: gate | up projection with the SwiGLU activation in its epilogue (the library's fused GEMV for <= 4 tokens, its
+    // tensor-core GEMM above; the same rounding points as the two launches they replace, which remain the fallback)
+    bool fused = false;
+    if (!f32 && T <= 4) {
+      pk_b200_gemv_args g{};
+      g.W = (const pk_bf16*)L.gate_up.d.ptr;
+      g.X = (const pk_bf16*)xa.ptr;
+      g.Y[0] = (pk_bf16*)act.ptr;
+      g.seg_rows[0] = a.ff;
+      g.M = a.ff;
+      g.N = T;
+      g.K = W;
+      g.epi = 1;
+      fused = k.pk_b200_gemv_fused(&g, st) == 0;
+    } else if (!f32) {
+      fused = k.pk_b200_gemm_swiglu((const pk_bf16*)L.gate_up.d.ptr, (const pk_bf16*)xa.ptr, (pk_bf16*)act.ptr, a.ff, T, W, st) == 0;
+    }
+    if (!fused) {
+      if (!lin(L.gate_up, xa.ptr, gu.ptr, T)) return false;
+      if (!rc(k.pk_act(gu.ptr, act.ptr, a.ff, T, 0, f32, st), "SwiGLU")) return false;
+    }
     if (!lin(L.down, act.ptr, mix.ptr, T)) return false;
     if (!rc(k.pk_res32_offset_norm_add(mix.ptr, f32, L.norm2.d.ptr, (float*)x.ptr, xa.ptr, W, T, c.eps, f32, st), "norm2")) return false;
   } else if (a.mlp_kind == 2) {

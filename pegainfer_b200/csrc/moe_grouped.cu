@@ -7,14 +7,14 @@
 //   2. moe_grouped_gemm<0>   hid[slot] = relu(W_up[e] x[token(slot)])^2          (rows gathered through the slot list)
 //   3. moe_grouped_gemm<1>   part[slot] = weight(pair) * W_down[e] hid[slot]     (fp32)
 //   4. moe_combine_kernel    y[t] = sum_k part[slot(t, k)] (+ logistic(g_t) * shared[t]), summed in the order of k
-// GEMM tiles: 64 rows x 64 outputs x 32 deep, 4 warps of 32 x 32, mma.sync m16n8k16 bf16 with fp32 accumulation, operands
+// GEMM tiles: 64 rows x 64 outputs x 64 deep, 4 warps of 32 x 32, mma.sync m16n8k16 bf16 with fp32 accumulation, operands
 // through a two-stage cp.async ring.  Tensor-bound: 4 * pairs * ff * width flop per layer.
 #include "common.cuh"
 #include "mma.cuh"
 
 namespace pk {
 
-constexpr int kGT = 64, kGK = 32, kGLd = kGK + 8;
+constexpr int kGT = 64, kGK = 64, kGLd = kGK + 8, kGPieces = kGT * kGK / 8 / 128;  // 16-byte pieces per thread, operand and k tile
 
 // meta layout (ints): [0] number of row tiles, [1 .. E+1] offsets (exclusive scan, E + 1 entries), then tile_expert[max_tiles],
 // tile_row0[max_tiles]; slot_pair[pairs] and pair_slot[pairs] are separate arrays.
@@ -72,14 +72,14 @@ __global__ void __launch_bounds__(128) moe_grouped_gemm_kernel(const bf16* __res
   const int m_end = off[e + 1], n0 = blockIdx.x * kGT;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tq = lane & 3, wm = warp >> 1, wn = warp & 1;
   const bf16* We = W + (size_t)e * N * K;
-  // each thread copies two 16-byte pieces of A and two of B per k tile
-  const bf16* a_src[2];
-  const bf16* b_src[2];
-  int kc[2], sm_off[2];
+  // each thread copies kGPieces 16-byte pieces of A and of B per k tile
+  const bf16* a_src[kGPieces];
+  const bf16* b_src[kGPieces];
+  int kc[kGPieces], sm_off[kGPieces];
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int c = tid + i * 128, r = c >> 2;
-    kc[i] = (c & 3) * 8;
+  for (int i = 0; i < kGPieces; ++i) {
+    const int c = tid + i * 128, r = c / (kGK / 8);
+    kc[i] = (c % (kGK / 8)) * 8;
     sm_off[i] = r * kGLd + kc[i];
     const int s = m0 + r;
     a_src[i] = s < m_end ? A + (size_t)(gather_div ? slot_pair[s] / gather_div : s) * K : nullptr;
@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(128) moe_grouped_gemm_kernel(const bf16* __res
   }
   auto load = [&](int kt, int buf) {
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kGPieces; ++i) {
       const int k = kt * kGK + kc[i];
       if (a_src[i] && k < K) cp_async16(&As[buf][sm_off[i]], a_src[i] + k);
       else *reinterpret_cast<uint4*>(&As[buf][sm_off[i]]) = make_uint4(0, 0, 0, 0);
