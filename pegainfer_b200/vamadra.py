@@ -270,8 +270,10 @@ class VamadraModel:
         shapes = weight_shapes(cfg)
         seen = set()
         for name, t in (weights.items() if isinstance(weights, dict) else weights):
-            if name not in shapes:
-                raise KeyError(f"{name}: not a tensor of this configuration")
+            if name not in shapes:  # nothing in the configuration uses it: leave it out, loudly
+                import warnings
+                warnings.warn(f"{name}: not a tensor of this configuration, ignored")
+                continue
             if tuple(t.shape) != tuple(shapes[name]):
                 raise ValueError(f"{name}: shape {tuple(t.shape)} != {tuple(shapes[name])} from the configuration")
             if t.is_cuda:
