@@ -822,7 +822,7 @@ def run_arch_compare(args):
             vm.step([(r, [7]) for r in rids], sample=True)
             res[f"decode_bs{bs}_launches_per_step"] = vm.launch_count()
             vm.use_graph(True)
-            t = med(lambda: vm.step([(r, [7]) for r in rids], sample=True))
+            t = med(lambda: vm.step([(r, [7]) for r in rids], sample=True, logits=False))  # tokens back, as the Qwen3 arm
             res[f"decode_bs{bs}_ctx{ctx}_tok_s"] = round(bs / t, 1)
             for r in rids:
                 vm.drop_request(r)

@@ -27,7 +27,7 @@ __global__ void rope_slice_kernel(const E* __restrict__ in, E* __restrict__ out,
   pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   const int t = blockIdx.x, half = dims / 2;
   const float p = (float)pos[t];
-  for (int e = threadIdx.x; e < heads * width; e += blockDim.x) {
+  for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < heads * width; e += gridDim.y * blockDim.x) {
     const int h = e / width, i = e % width;
     const E* src = in + ((size_t)t * heads + h) * in_stride + in_off;
     float r;
@@ -168,11 +168,12 @@ using namespace pk;
 extern "C" int pk_rope_slice(const void* in, void* out, const int* positions, const float* freq, float mag, int tokens, int heads, int in_stride,
                              int in_off, int out_stride, int out_off, int width, int dims, int f32, pk_stream st) {
   if (!in || !out || !positions || !freq || tokens <= 0 || heads <= 0 || width <= 0 || dims < 0 || dims > width || (dims & 1)) return -1;
+  const dim3 rope_grid(tokens, tokens >= 64 ? 1 : (heads * width + 127) / 128);  // few tokens: spread one token over CTAs
   if (f32)
-    launch(rope_slice_kernel<float>, dim3(tokens), dim3(128), 0, st, true, (const float*)in, (float*)out, positions, freq, mag, heads, in_stride,
+    launch(rope_slice_kernel<float>, rope_grid, dim3(128), 0, st, true, (const float*)in, (float*)out, positions, freq, mag, heads, in_stride,
            in_off, out_stride, out_off, width, dims);
   else
-    launch(rope_slice_kernel<bf16>, dim3(tokens), dim3(128), 0, st, true, (const bf16*)in, (bf16*)out, positions, freq, mag, heads, in_stride, in_off,
+    launch(rope_slice_kernel<bf16>, rope_grid, dim3(128), 0, st, true, (const bf16*)in, (bf16*)out, positions, freq, mag, heads, in_stride, in_off,
            out_stride, out_off, width, dims);
   return (int)cudaGetLastError();
 }

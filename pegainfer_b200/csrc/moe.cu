@@ -127,7 +127,8 @@ __global__ void moe_down_kernel(const E* __restrict__ hid, const E* __restrict__
   pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int ffp = (ff + 3) & ~3;
-  for (int i = threadIdx.x; i < top * ff; i += blockDim.x) hs[(i / ff) * ffp + i % ff] = to_f(hid[(size_t)t * top * ff + i]);
+  for (int k = 0; k < top; ++k)
+    for (int f = threadIdx.x; f < ff; f += blockDim.x) hs[k * ffp + f] = to_f(hid[((size_t)t * top + k) * ff + f]);
   __syncthreads();
   const float g = shared ? 1.f / (1.f + expf(-sg[t])) : 0.f;
   const int i_end = min(width, (int)(blockIdx.y + 1) * kMoeDownRowsPerBlock);

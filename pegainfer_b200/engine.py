@@ -72,7 +72,7 @@ class Engine:
                 if n not in self.slots:
                     self.slots[n] = self.model.alloc_request()
                 batch.append((self.slots[n], t))
-            _, sampled = self.model.step(batch, [w for _, _, w in entries], sample=True)
+            _, sampled = self.model.step(batch, [w for _, _, w in entries], sample=True, logits=False)
             row = 0
             for (i, kind) in kinds:
                 if kind == "part":

@@ -336,10 +336,11 @@ class VamadraModel:
         return list(buf[:max(n, 0)])
 
     # -- one engine step
-    def step(self, entries, want=None, sample: bool = False):
+    def step(self, entries, want=None, sample: bool = False, logits: bool = True):
         """``entries``: [(request id, [token, ...]), ...] -- each request's next tokens (a portion of its prompt or one decoded
         token); all entries run as one batch.  ``want``: per entry the offsets inside its tokens whose logits are wanted
-        (default: the last one).  Returns fp32 logits [rows, vocab] on the host in entry order (and greedy tokens with ``sample``)."""
+        (default: the last one).  Returns fp32 logits [rows, vocab] on the host in entry order (and greedy tokens with ``sample``);
+        ``logits=False`` leaves the logits on the device and returns ``None`` in their place (a generation loop needs the tokens only)."""
         n = len(entries)
         flat, lens, rids, rows, base = [], [], [], [], 0
         for i, (rid, toks) in enumerate(entries):
@@ -349,10 +350,10 @@ class VamadraModel:
             lens.append(len(toks))
             rids.append(int(rid))
             base += len(toks)
-        out = torch.empty((len(rows), self.cfg.vocab), dtype=torch.float32)
+        out = torch.empty((len(rows), self.cfg.vocab), dtype=torch.float32) if logits else None
         sampled = (C.c_int * max(len(rows), 1))()
         self._ck(self._h.pv_step(self._m, n, (C.c_int * len(flat))(*flat), (C.c_int * n)(*lens), (C.c_int * n)(*rids), len(rows),
-                                 (C.c_int * max(len(rows), 1))(*rows), int(sample), out.data_ptr() if len(rows) else None, sampled))
+                                 (C.c_int * max(len(rows), 1))(*rows), int(sample), out.data_ptr() if logits and len(rows) else None, sampled))
         return (out, list(sampled)[:len(rows)]) if sample else out
 
     def generate(self, prompt: list[int], max_tokens: int):

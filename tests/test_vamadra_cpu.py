@@ -70,7 +70,7 @@ class FakeModel:
         del self.len[rid]
         self.free.append(rid)
 
-    def step(self, entries, want=None, sample=False):
+    def step(self, entries, want=None, sample=False, logits=True):
         assert len({r for r, _ in entries}) == len(entries) and all(r in self.len for r, _ in entries)
         self.steps.append([(r, list(t)) for r, t in entries])
         rows = []
