@@ -713,6 +713,55 @@ def test_captured_decode_steps_equal_eager_ones(dtype, oracle_cache):
         assert close(outs[True][:, 0], want_a[500:530], dtype)
 
 
+def random_cfg(seed):
+    """a configuration drawn at random: sizes that are and are not multiples of 8 / 16 / 64, every kind of layer, in any order"""
+    r = np.random.RandomState(seed)
+    pick = lambda xs: xs[r.randint(len(xs))]
+    width, layers, owners = int(pick([40, 56, 100, 128, 72])), [], []
+    for i in range(int(r.randint(2, 6))):
+        if owners and r.rand() < 0.4:
+            src = int(pick(owners))
+            mx = dict(layers[src]["mixer"], kv_from=src, heads=int(r.randint(1, 9)), dim=int(pick([8, 12, 32])), vdim=int(pick([8, 20, 32])))
+            mx["scale"] = float(r.uniform(0.1, 0.3))
+        else:
+            rot = int(pick([4, 8, 16, 32]))
+            mx = mixer(int(r.randint(1, 9)), int(pick([8, 12, 32, 64])), rot, int(pick([8, 20, 64])), int(pick([16, 24, 64, 128, 192])),
+                       scaling=bool(r.rand() < 0.5), base=float(pick([100.0, 10000.0, 250000.0])))
+            owners.append(i)
+        kind = pick(["dense", "moe", "moe", None])
+        if kind == "dense":
+            mlp = {"kind": "dense", "ff": int(pick([24, 50, 96, 160]))}
+        elif kind == "moe":
+            count = int(pick([1, 2, 4]))
+            per = int(pick([1, 2, 3]))
+            keep = int(r.randint(1, count + 1))
+            mlp = moe(count * per, int(r.randint(1, keep * per + 1)), count, keep, int(pick([8, 20, 48])), int(pick([0, 16, 40])),
+                      scale=float(pick([1.0, 2.5])))
+        else:
+            mlp = None
+        layers.append(layer(mx, mlp))
+    return {"architecture": "Vamadra", "vocab": int(pick([50, 130, 257])), "width": width, "norm": {"eps": float(pick([1e-5, 1e-6]))}, "layers": layers}
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_configurations(seed):
+    """whatever the configuration says: float32 equals the oracle on a prompt cut into portions, bfloat16 stays within rounding"""
+    cfg = random_cfg(seed)
+    w = make_weights(cfg, 100 + seed, sharp=3.0)
+    toks = tokens_for(cfg, 90, 200 + seed)
+    want = O.forward(cfg, w, toks)
+    for dtype in (F32, BF16):
+        m = build(cfg, w, dtype, max_tokens=128)
+        rid, outs, at = m.alloc_request(), [], 0
+        for n in (37, 2, 40, 1, 1, 9):
+            outs.append(m.step([(rid, toks[at:at + n])], [list(range(n))]))
+            at += n
+        got = torch.cat(outs)
+        assert torch.isfinite(got).all()
+        assert close(got, want, dtype) if dtype == F32 else row_errors(got, want).median().item() < 0.08, (seed, cfg)
+        m.close()
+
+
 def greedy_oracle(cfg, w, prompt, n):
     toks = list(prompt)
     for _ in range(n):
