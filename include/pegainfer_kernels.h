@@ -463,6 +463,59 @@ long pk_moe_grouped_workspace_bytes(int tokens, int top, int experts, int width,
 int pk_moe_grouped_relu2(const void* xa, const void* w_up, const void* w_down, const int* ids, const float* weights, const void* shared,
                          const float* shared_gate, float* y, void* workspace, int tokens, int top, int experts, int width, int ff, pk_stream st);
 
+/* =============== parallel pre-norm blocks, grouped-query attention with sink / chunks, recurrent mixers ===============
+ * More building blocks on the same conventions (fp32 residual, element type behind void pointers chosen by `f32`,
+ * ragged batches described by per-token `positions` / `req` and per-entry arrays).  Small parameter vectors that enter
+ * fp32 arithmetic only (alpha, correction, gate biases, decay parameters) are float arrays. */
+/* x[t] = float(embed[ids[t]]) * scale */
+int pk_res32_embed_scaled(const void* embed, const int* token_ids, float* x, int width, int tokens, float scale, int f32, pk_stream st);
+/* Dynamic Tanh norm fused with the residual sum of a parallel block: x += (ya + yf) (either may be NULL; ya element type, yf float), then
+ * h = tanh(alpha[0] * x) * w + b in the element type and, when h32 != NULL, unrounded.  w == NULL: only the sum. */
+int pk_res32_add_dyt(const void* ya, const float* yf, const float* alpha, const void* w, const void* b, float* x, void* h, float* h32, int width,
+                     int tokens, int f32, pk_stream st);
+/* out[r] = dyt(x[rows[r]]) in the element type (last norm, only for the rows whose logits are wanted) */
+int pk_res32_dyt_rows(const float* x, const int* rows, const float* alpha, const void* w, const void* b, void* out, int width, int n_rows, int f32,
+                      pk_stream st);
+/* out = float(in) * scale */
+int pk_scale_to_f32(const void* in, int in_f32, float* out, long n, float scale, pk_stream st);
+/* Grouped-query attention over a paged cache (gqa_attention.cu).  qkv [tokens, ld] = [q heads*dim | k kv_heads*dim | v kv_heads*vdim] (+ bias of the
+ * same layout, may be NULL); q and k rotate over their first `dims` entries by positions[t] * freq[i] (cos, sin times mag), pairs (2i, 2i+1) when
+ * `interleaved`, else (i, i + dims/2).  q goes to q_out [tokens, heads*dim]; k | v into the cache: page pages[page_off[req[t]] + p / page_size],
+ * slot p % page_size, kv_heads*(dim+vdim) elements per slot. */
+int pk_gqa_rope_append(const void* qkv, int ld, const void* bias, const int* positions, const int* req, const int* page_off, const int* pages,
+                       void* q_out, void* cache, long page_stride, int page_size, int heads, int kv_heads, int dim, int vdim, int dims,
+                       int interleaved, const float* freq, float mag, int tokens, int f32, pk_stream st);
+/* out[t,h] = softmax_j(q[t,h] . k_j * scale; exp(sink[h]) added to the denominator when sink != NULL) v_j over the request's cached positions
+ * lo(p) <= j <= p, lo(p) = floor(p / chunk) * chunk (chunk 0: from the start).  Tokens of one request are contiguous with ascending positions. */
+int pk_gqa_attention(const void* q, const void* cache, const void* sink, const int* positions, const int* req, const int* page_off,
+                     const int* pages, void* out, long page_stride, int page_size, int tokens, int heads, int kv_heads, int dim, int vdim,
+                     float scale, int chunk, int f32, pk_stream st);
+/* Recurrent mixers (recurrent_mixers.cu).  Entry e of the step owns rows [row0[e], row0[e] + len[e]) and the state slot slot[e] (floats at
+ * state + slot * slot_stride).  Short causal convolution + SiLU per channel; the slot keeps the last taps - 1 inputs [taps-1][channels]. */
+int pk_causal_conv_silu(const void* in, int ld_in, const void* w, float* state, long slot_stride, const int* req, const int* slot, const int* row0,
+                        const int* len, void* out, int ld_out, int channels, int taps, int tokens, int entries, int f32, pk_stream st);
+/* Gated delta rule over each entry's rows.  qkv [tokens, ld] holds q / k (kv_heads x dim) and v (heads x vdim) at the given offsets; z [tokens, ldz]
+ * fp32 holds the decay and write-strength projections (one per head) at decay_off / beta_off.  State S [heads][dim][vdim]; out fp32 [tokens, heads*vdim]. */
+int pk_gated_delta_seq(const void* qkv, int ld, int q_off, int k_off, int v_off, const float* z, int ldz, int decay_off, int beta_off,
+                       const float* a_log, const float* dt_bias, float* state, long slot_stride, const int* slot, const int* row0, const int* len,
+                       float* out, int heads, int kv_heads, int dim, int vdim, int entries, int f32, pk_stream st);
+/* xLSTM matrix memory over each entry's rows; state S [heads][dim][vdim], n [heads][dim], m [heads][vdim + 1]; out fp32 numerator, den [tokens, heads]. */
+int pk_mlstm_seq(const void* qkv, int ld, int q_off, int k_off, int v_off, const float* z, int ldz, int forget_off, int input_off,
+                 const float* input_bias, const float* forget_bias, float cap, float* state, long slot_stride, const int* slot, const int* row0,
+                 const int* len, float* out, float* den, int heads, int dim, int vdim, int entries, int f32, pk_stream st);
+/* out[t,h,:] = rms_norm(o[t,h,:] / den[t,h]) * w[h * w_stride + :] * act(gate[t, gate_off + h*vdim + :]); act 0 silu, 1 logistic; den may be NULL */
+int pk_head_norm_gate(const float* o, const float* den, const void* w, int w_stride, const void* gate, int ld_gate, int gate_off, void* out, int tokens,
+                      int heads, int vdim, float eps, int act, int f32, pk_stream st);
+/* Router with options (moe.cu): logits rows of stride ld; score_kind 0 softmax / 1 logistic; correction (may be NULL) added for the choice only;
+ * group_top 1: a group scores as its best expert, 2: as the sum of its two best; renorm 1: weights divided by their sum; weights times scale. */
+int pk_router_topk_ex(const float* logits, int ld, const float* correction, int* ids, float* weights, int tokens, int experts, int top, int groups,
+                      int keep, float scale, int score_kind, int group_top, int renorm, pk_stream st);
+/* Experts with a choice of activation: act 0 relu^2 (W_up [experts, ff, width]); act 1 gated, silu(gate) * up, W_up [experts, 2 ff, width] with gate
+ * and up rows interleaved (2f, 2f + 1). */
+int pk_moe_up_act(const void* xa, const void* w_up, const int* ids, void* hid, int tokens, int top, int width, int ff, int act, int f32, pk_stream st);
+int pk_moe_grouped_act(const void* xa, const void* w_up, const void* w_down, const int* ids, const float* weights, const void* shared,
+                       const float* shared_gate, float* y, void* workspace, int tokens, int top, int experts, int width, int ff, int act, pk_stream st);
+
 #ifdef __cplusplus
 }
 #endif

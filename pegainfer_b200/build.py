@@ -44,7 +44,9 @@ def _run(cmd: list[str]) -> None:
 # others): kernel sources, host sources.  A later full build adds the rest and links both libraries again.
 PARTS_OF = {
     "Vamadra": (("runtime.cu", "gemm.cu", "gemm2.cu", "gemv.cu", "sampling.cu", "residual32_ops.cu", "gemm_batched_mma.cu", "latent_attention.cu", "latent_attention_mma.cu", "moe.cu", "moe_grouped.cu"),
-                ("qwen3_host.cpp", "vamadra_host.cpp")),
+                ("qwen3_host.cpp", "layered_host.cpp")),
+    "Risolorn": (("runtime.cu", "gemm.cu", "gemm2.cu", "gemv.cu", "sampling.cu", "residual32_ops.cu", "gemm_batched_mma.cu", "gqa_attention.cu", "recurrent_mixers.cu", "moe.cu", "moe_grouped.cu"),
+                 ("qwen3_host.cpp", "layered_host.cpp")),
 }
 MANIFEST = os.path.join(OBJ, "linked.txt")
 

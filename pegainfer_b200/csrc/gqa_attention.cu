@@ -1,0 +1,339 @@
+// Grouped-query softmax attention over a paged K/V cache for ragged batches, with the options that newer decoder
+// designs combine: projection biases, a rotary embedding over the first `dims` entries of each head from a frequency
+// table (pairs interleaved (2i, 2i+1) or split in halves (i, i + dims/2); plain, YaRN or any other schedule is the
+// host's table), a chunk-local causal mask (query at position p sees keys floor(p / chunk) * chunk .. p; chunk 0 = plain
+// causal) and a learned per-head sink that adds exp(sink) to the softmax denominator without a value.
+//
+// Cache: token at position p of a request lives in page pages[page_off[req] + p / page_size], slot p % page_size, at
+//   cache + page * page_stride + slot * (G * dim + G * vdim):  [K of G heads | V of G heads].
+// Element type E (bf16 or float) for activations / cache / weights; scores, softmax and accumulation are fp32.
+//   gqa_rope_append_kernel      bias + rotation of q and k, q to its buffer, k / v into the cache.  HBM-bound.
+//   gqa_attention_kernel        one CTA per (query row, query head): warps stride over the visible keys with an online
+//                               softmax each (lanes split the features), merged with the sink at the end.  Any sizes.
+//   gqa_attention_mma_kernel    bf16 prompt portions on the tensor cores (64 query rows of one head per CTA).
+#include "common.cuh"
+#include "mma.cuh"
+#include "typed.cuh"
+
+namespace pk {
+
+// qkv [tokens, ld] = [q (H*dim) | k (G*dim) | v (G*vdim)] rows of the stacked projection; bias (same layout) may be null.
+template <typename E>
+__global__ void gqa_rope_append_kernel(const E* __restrict__ qkv, int ld, const E* __restrict__ bias, const int* __restrict__ pos,
+                                       const int* __restrict__ req, const int* __restrict__ page_off, const int* __restrict__ pages,
+                                       E* __restrict__ q_out, E* __restrict__ cache, long page_stride, int page_size, int H, int G, int dim, int vdim,
+                                       int dims, int interleaved, const float* __restrict__ freq, float mag) {
+  pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
+  const int t = blockIdx.x, p = pos[t];
+  const E* row = qkv + (size_t)t * ld;
+  const int nq = H * dim, nk = G * dim, nv = G * vdim, half = dims >> 1;
+  E* slot = cache + (size_t)pages[page_off[req[t]] + p / page_size] * page_stride + (size_t)(p % page_size) * (nk + nv);
+  for (int e = threadIdx.x; e < nq + nk + nv; e += blockDim.x) {
+    float v = to_f(row[e]) + (bias ? to_f(bias[e]) : 0.f);
+    if (e < nq + nk) {
+      const int d = (e < nq ? e : e - nq) % dim;
+      if (d < dims) {
+        int i, pe;
+        bool first;
+        if (interleaved) {
+          i = d >> 1;
+          first = (d & 1) == 0;
+          pe = first ? e + 1 : e - 1;
+        } else {
+          first = d < half;
+          i = first ? d : d - half;
+          pe = first ? e + half : e - half;
+        }
+        const float o = to_f(row[pe]) + (bias ? to_f(bias[pe]) : 0.f);
+        const float a = (float)p * freq[i];
+        const float c = cosf(a) * mag, s = sinf(a) * mag;
+        v = first ? v * c - o * s : v * c + o * s;
+      }
+    }
+    if (e < nq) q_out[(size_t)t * nq + e] = from_f<E>(v);
+    else slot[e - nq] = from_f<E>(v);
+  }
+}
+
+constexpr int kGqaWarps = 4;
+constexpr int kGqaMaxPerLane = 8;  // features per lane: dim, vdim <= 256
+
+template <typename E>
+__global__ void __launch_bounds__(kGqaWarps * 32) gqa_attention_kernel(const E* __restrict__ q, const E* __restrict__ cache, const E* __restrict__ sink,
+                                                                      const int* __restrict__ pos, const int* __restrict__ req,
+                                                                      const int* __restrict__ page_off, const int* __restrict__ pages,
+                                                                      E* __restrict__ out, long page_stride, int page_size, int H, int G, int dim,
+                                                                      int vdim, float scale, int chunk) {
+  __shared__ float sm_m[kGqaWarps], sm_l[kGqaWarps];
+  extern __shared__ float sm_acc[];  // [warps][vdim]
+  pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
+  const int t = blockIdx.x, h = blockIdx.y, g = h / (H / G), lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int p = pos[t], lo = chunk > 0 ? (p / chunk) * chunk : 0;
+  const int* pg = pages + page_off[req[t]];
+  const int tok = G * (dim + vdim);
+  float qr[kGqaMaxPerLane], acc[kGqaMaxPerLane];
+#pragma unroll
+  for (int i = 0; i < kGqaMaxPerLane; ++i) {
+    const int d = lane + 32 * i;
+    qr[i] = d < dim ? to_f(q[((size_t)t * H + h) * dim + d]) * scale : 0.f;
+    acc[i] = 0.f;
+  }
+  float m = -INFINITY, l = 0.f;
+  for (int j = lo + warp; j <= p; j += kGqaWarps) {
+    const E* kv = cache + (size_t)pg[j / page_size] * page_stride + (size_t)(j % page_size) * tok;
+    const E* kr = kv + g * dim;
+    const E* vr = kv + G * dim + g * vdim;
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < kGqaMaxPerLane; ++i) {
+      const int d = lane + 32 * i;
+      if (d < dim) s = fmaf(qr[i], to_f(kr[d]), s);
+    }
+    s = warp_sum(s);
+    const float mn = fmaxf(m, s), c = expf(m - mn), e = expf(s - mn);
+    l = l * c + e;
+#pragma unroll
+    for (int i = 0; i < kGqaMaxPerLane; ++i) {
+      const int d = lane + 32 * i;
+      if (d < vdim) acc[i] = acc[i] * c + e * to_f(vr[d]);
+    }
+    m = mn;
+  }
+  if (lane == 0) {
+    sm_m[warp] = m;
+    sm_l[warp] = l;
+  }
+#pragma unroll
+  for (int i = 0; i < kGqaMaxPerLane; ++i) {
+    const int d = lane + 32 * i;
+    if (d < vdim) sm_acc[warp * vdim + d] = acc[i];
+  }
+  __syncthreads();
+  const float sk = sink ? to_f(sink[h]) : -INFINITY;
+  float mt = sk;
+#pragma unroll
+  for (int w = 0; w < kGqaWarps; ++w) mt = fmaxf(mt, sm_m[w]);
+  float den = sink ? expf(sk - mt) : 0.f;
+  float cw[kGqaWarps];
+#pragma unroll
+  for (int w = 0; w < kGqaWarps; ++w) {
+    cw[w] = sm_m[w] == -INFINITY ? 0.f : expf(sm_m[w] - mt);
+    den += sm_l[w] * cw[w];
+  }
+  for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
+    float o = 0.f;
+#pragma unroll
+    for (int w = 0; w < kGqaWarps; ++w) o += sm_acc[w * vdim + d] * cw[w];
+    out[((size_t)t * H + h) * vdim + d] = from_f<E>(o / den);
+  }
+}
+
+// ---- tensor cores (bf16): one CTA = 64 consecutive rows of the step (4 warps x 16 rows) for one query head.  Rows of a
+// tile may belong to several requests: the tile walks each request's visible key range in 64-key blocks with the other
+// rows masked.  dim, vdim multiples of 16 up to 128.  K and V blocks are staged in shared memory; S = Q K^T and O += P V
+// with mma.sync m16n8k16, P rounded to bf16 for the second product, statistics in fp32.
+constexpr int kAmRows = 64, kAmKeys = 64;
+
+template <int DQ, int DV>
+__global__ void __launch_bounds__(128) gqa_attention_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache, const bf16* __restrict__ sink,
+                                                               const int* __restrict__ pos, const int* __restrict__ req,
+                                                               const int* __restrict__ page_off, const int* __restrict__ pages,
+                                                               bf16* __restrict__ out, long page_stride, int page_size, int T, int H, int G,
+                                                               float scale, int chunk) {
+  constexpr int LDK = DQ + 8, LDV = DV + 8;
+  __shared__ __align__(16) bf16 Ks[kAmKeys * LDK];
+  __shared__ __align__(16) bf16 Vs[kAmKeys * LDV];
+  __shared__ int s_req[kAmRows], s_pos[kAmRows];
+  pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
+  const int t0 = blockIdx.x * kAmRows, h = blockIdx.y, g = h / (H / G);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gq = lane >> 2, tq = lane & 3;
+  if (tid < kAmRows) {
+    const int t = t0 + tid;
+    s_req[tid] = t < T ? req[t] : -1;
+    s_pos[tid] = t < T ? pos[t] : -1;
+  }
+  __syncthreads();
+  const int tok = G * (DQ + DV);
+  // this warp's rows: r0 = warp * 16 + gq and r0 + 8
+  const int ra = warp * 16 + gq, rb = ra + 8;
+  const int req_a = s_req[ra], req_b = s_req[rb], pos_a = s_pos[ra], pos_b = s_pos[rb];
+  const int lo_a = chunk > 0 && pos_a >= 0 ? (pos_a / chunk) * chunk : 0, lo_b = chunk > 0 && pos_b >= 0 ? (pos_b / chunk) * chunk : 0;
+  // Q fragments (A operand, row-major 16 x DQ)
+  uint32_t qa[DQ / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < DQ / 16; ++kk) {
+    const int c = kk * 16 + 2 * tq;
+    const bf16* qra = q + ((size_t)(t0 + ra) * H + h) * DQ + c;
+    const bf16* qrb = q + ((size_t)(t0 + rb) * H + h) * DQ + c;
+    qa[kk][0] = req_a >= 0 ? *reinterpret_cast<const uint32_t*>(qra) : 0u;
+    qa[kk][1] = req_b >= 0 ? *reinterpret_cast<const uint32_t*>(qrb) : 0u;
+    qa[kk][2] = req_a >= 0 ? *reinterpret_cast<const uint32_t*>(qra + 8) : 0u;
+    qa[kk][3] = req_b >= 0 ? *reinterpret_cast<const uint32_t*>(qrb + 8) : 0u;
+  }
+  float oa[DV / 8][4] = {};
+  float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+  // requests of the tile are contiguous runs: walk them one after the other
+  int r_first = 0;
+  while (r_first < kAmRows && s_req[r_first] >= 0) {
+    const int rq = s_req[r_first];
+    int r_last = r_first;
+    while (r_last + 1 < kAmRows && s_req[r_last + 1] == rq) ++r_last;
+    const int p_min = s_pos[r_first], p_max = s_pos[r_last];
+    const int k_lo = chunk > 0 ? (p_min / chunk) * chunk : 0;
+    const int* pg = pages + page_off[rq];
+    for (int k0 = k_lo - (k_lo % kAmKeys); k0 <= p_max; k0 += kAmKeys) {
+      __syncthreads();  // the previous block's readers are done
+      for (int c = tid; c < kAmKeys * (DQ / 8); c += 128) {
+        const int r = c / (DQ / 8), cc = (c % (DQ / 8)) * 8, j = k0 + r;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (j <= p_max && j >= k_lo) v = *reinterpret_cast<const uint4*>(cache + (size_t)pg[j / page_size] * page_stride + (size_t)(j % page_size) * tok + g * DQ + cc);
+        *reinterpret_cast<uint4*>(&Ks[r * LDK + cc]) = v;
+      }
+      for (int c = tid; c < kAmKeys * (DV / 8); c += 128) {
+        const int r = c / (DV / 8), cc = (c % (DV / 8)) * 8, j = k0 + r;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (j <= p_max && j >= k_lo) v = *reinterpret_cast<const uint4*>(cache + (size_t)pg[j / page_size] * page_stride + (size_t)(j % page_size) * tok + G * DQ + g * DV + cc);
+        *reinterpret_cast<uint4*>(&Vs[r * LDV + cc]) = v;
+      }
+      __syncthreads();
+      const bool on_a = req_a == rq, on_b = req_b == rq;
+      if (!__any_sync(0xffffffffu, on_a || on_b)) continue;  // warp-uniform: the tensor-core instructions below need all 32 lanes
+      // S = Q K^T: 16 rows x 64 keys per warp
+      float s[kAmKeys / 8][4] = {};
+#pragma unroll
+      for (int kk = 0; kk < DQ / 16; ++kk)
+#pragma unroll
+        for (int np = 0; np < kAmKeys / 16; ++np) {
+          uint32_t b[4];
+          ldsm_x4(b, &Ks[(np * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * LDK + kk * 16 + ((lane >> 3) & 1) * 8]);
+          mma_bf16_16816(s[np * 2], qa[kk], b[0], b[1]);
+          mma_bf16_16816(s[np * 2 + 1], qa[kk], b[2], b[3]);
+        }
+      float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+      for (int ni = 0; ni < kAmKeys / 8; ++ni)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = k0 + ni * 8 + 2 * tq + (e & 1);
+          const bool top = e < 2;
+          const bool ok = top ? (on_a && j <= pos_a && j >= lo_a) : (on_b && j <= pos_b && j >= lo_b);
+          const float v = ok ? s[ni][e] * scale : -INFINITY;
+          s[ni][e] = v;
+          if (top) mx_a = fmaxf(mx_a, v);
+          else mx_b = fmaxf(mx_b, v);
+        }
+      mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+      mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+      mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+      mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+      const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+      const float c_a = mn_a == -INFINITY ? 1.f : expf(m_a - mn_a), c_b = mn_b == -INFINITY ? 1.f : expf(m_b - mn_b);
+      float sum_a = 0.f, sum_b = 0.f;
+      uint32_t pa[kAmKeys / 16][4];
+#pragma unroll
+      for (int ni = 0; ni < kAmKeys / 8; ++ni) {
+        const float e0 = mn_a == -INFINITY ? 0.f : expf(s[ni][0] - mn_a), e1 = mn_a == -INFINITY ? 0.f : expf(s[ni][1] - mn_a);
+        const float e2 = mn_b == -INFINITY ? 0.f : expf(s[ni][2] - mn_b), e3 = mn_b == -INFINITY ? 0.f : expf(s[ni][3] - mn_b);
+        const float r0 = round_bf16(e0), r1 = round_bf16(e1), r2 = round_bf16(e2), r3 = round_bf16(e3);
+        sum_a += r0 + r1;
+        sum_b += r2 + r3;
+        pa[ni >> 1][(ni & 1) * 2] = pack_bf16(r0, r1);
+        pa[ni >> 1][(ni & 1) * 2 + 1] = pack_bf16(r2, r3);
+      }
+      sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 1);
+      sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 2);
+      sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 1);
+      sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 2);
+      l_a = l_a * c_a + sum_a;
+      l_b = l_b * c_b + sum_b;
+      m_a = mn_a;
+      m_b = mn_b;
+#pragma unroll
+      for (int ni = 0; ni < DV / 8; ++ni) {
+        oa[ni][0] *= c_a;
+        oa[ni][1] *= c_a;
+        oa[ni][2] *= c_b;
+        oa[ni][3] *= c_b;
+      }
+      // O += P V: V block is [keys][DV] row-major = the B operand's k-major form through ldmatrix.trans
+#pragma unroll
+      for (int kk = 0; kk < kAmKeys / 16; ++kk)
+#pragma unroll
+        for (int np = 0; np < DV / 16; ++np) {
+          uint32_t b[4];
+          ldsm_x4_trans(b, &Vs[(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDV + np * 16 + ((lane >> 4) & 1) * 8]);
+          mma_bf16_16816(oa[np * 2], pa[kk], b[0], b[1]);
+          mma_bf16_16816(oa[np * 2 + 1], pa[kk], b[2], b[3]);
+        }
+    }
+    r_first = r_last + 1;
+  }
+  const float sk = sink ? bf2f(sink[h]) : -INFINITY;
+  const float mt_a = fmaxf(m_a, sk), mt_b = fmaxf(m_b, sk);
+  const float f_a = m_a == -INFINITY ? 0.f : expf(m_a - mt_a), f_b = m_b == -INFINITY ? 0.f : expf(m_b - mt_b);
+  const float d_a = l_a * f_a + (sink ? expf(sk - mt_a) : 0.f), d_b = l_b * f_b + (sink ? expf(sk - mt_b) : 0.f);
+  const float i_a = f_a / d_a, i_b = f_b / d_b;
+#pragma unroll
+  for (int ni = 0; ni < DV / 8; ++ni) {
+    const int c = ni * 8 + 2 * tq;
+    if (req_a >= 0) *reinterpret_cast<uint32_t*>(out + ((size_t)(t0 + ra) * H + h) * DV + c) = pack_bf16(oa[ni][0] * i_a, oa[ni][1] * i_a);
+    if (req_b >= 0) *reinterpret_cast<uint32_t*>(out + ((size_t)(t0 + rb) * H + h) * DV + c) = pack_bf16(oa[ni][2] * i_b, oa[ni][3] * i_b);
+  }
+}
+
+template <int DQ, int DV>
+static void launch_gqa_mma(const bf16* q, const bf16* cache, const bf16* sink, const int* pos, const int* req, const int* page_off, const int* pages,
+                           bf16* out, long page_stride, int page_size, int T, int H, int G, float scale, int chunk, cudaStream_t st) {
+  launch(gqa_attention_mma_kernel<DQ, DV>, dim3((T + kAmRows - 1) / kAmRows, H), dim3(128), 0, st, true, q, cache, sink, pos, req, page_off, pages, out,
+         page_stride, page_size, T, H, G, scale, chunk);
+}
+
+}  // namespace pk
+
+using namespace pk;
+
+extern "C" int pk_gqa_rope_append(const void* qkv, int ld, const void* bias, const int* positions, const int* req, const int* page_off,
+                                  const int* pages, void* q_out, void* cache, long page_stride, int page_size, int heads, int kv_heads, int dim,
+                                  int vdim, int dims, int interleaved, const float* freq, float mag, int tokens, int f32, pk_stream st) {
+  if (!qkv || !positions || !req || !page_off || !pages || !q_out || !cache || tokens <= 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads ||
+      dim <= 0 || vdim <= 0 || dims < 0 || dims > dim || (dims & 1) || (dims > 0 && !freq) || page_size <= 0)
+    return -1;
+  if (f32)
+    launch(gqa_rope_append_kernel<float>, dim3(tokens), dim3(256), 0, st, true, (const float*)qkv, ld, (const float*)bias, positions, req, page_off, pages,
+           (float*)q_out, (float*)cache, page_stride, page_size, heads, kv_heads, dim, vdim, dims, interleaved, freq, mag);
+  else
+    launch(gqa_rope_append_kernel<bf16>, dim3(tokens), dim3(256), 0, st, true, (const bf16*)qkv, ld, (const bf16*)bias, positions, req, page_off, pages,
+           (bf16*)q_out, (bf16*)cache, page_stride, page_size, heads, kv_heads, dim, vdim, dims, interleaved, freq, mag);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int pk_gqa_attention(const void* q, const void* cache, const void* sink, const int* positions, const int* req, const int* page_off,
+                                const int* pages, void* out, long page_stride, int page_size, int tokens, int heads, int kv_heads, int dim,
+                                int vdim, float scale, int chunk, int f32, pk_stream st) {
+  if (!q || !cache || !positions || !req || !page_off || !pages || !out || tokens <= 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads ||
+      dim <= 0 || vdim <= 0 || chunk < 0 || page_size <= 0)
+    return -1;
+  if (dim > 32 * kGqaMaxPerLane || vdim > 32 * kGqaMaxPerLane) return -2;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(cache) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
+                       page_stride % 8 == 0;
+  if (!f32 && tokens >= 32 && aligned && dim == vdim && (dim == 64 || dim == 128 || dim == 32)) {
+#define PK_GQA_MMA(D) \
+  launch_gqa_mma<D, D>((const bf16*)q, (const bf16*)cache, (const bf16*)sink, positions, req, page_off, pages, (bf16*)out, page_stride, page_size, tokens, heads, kv_heads, scale, chunk, st)
+    if (dim == 32) PK_GQA_MMA(32);
+    else if (dim == 64) PK_GQA_MMA(64);
+    else PK_GQA_MMA(128);
+#undef PK_GQA_MMA
+    return (int)cudaGetLastError();
+  }
+  const size_t smem = (size_t)kGqaWarps * vdim * sizeof(float);
+  if (f32)
+    launch(gqa_attention_kernel<float>, dim3(tokens, heads), dim3(kGqaWarps * 32), smem, st, true, (const float*)q, (const float*)cache, (const float*)sink,
+           positions, req, page_off, pages, (float*)out, page_stride, page_size, heads, kv_heads, dim, vdim, scale, chunk);
+  else
+    launch(gqa_attention_kernel<bf16>, dim3(tokens, heads), dim3(kGqaWarps * 32), smem, st, true, (const bf16*)q, (const bf16*)cache, (const bf16*)sink,
+           positions, req, page_off, pages, (bf16*)out, page_stride, page_size, heads, kv_heads, dim, vdim, scale, chunk);
+  return (int)cudaGetLastError();
+}

@@ -1,16 +1,22 @@
-// C++ host of the Vamadra design: a decoder whose layers are listed one by one in the checkpoint's configuration, each
-// with a latent-attention mixer (compressed paged cache, shared rotated key part, per-head softmax sink, logistic
-// output gate, optional reuse of an earlier layer's cache) and a dense or mixture-of-experts feed-forward, on an fp32
-// residual stream with the norm on the sublayer's output.
+// C++ host of the decoder designs whose checkpoint configuration lists the layers one by one (Vamadra, Risolorn), on an fp32
+// residual stream.  A layer is a mixer plus an optional feed-forward, put together in one of two block forms:
+//   block 0  sequential sublayers with the norm on each sublayer's OUTPUT:  x += norm(mixer(x));  x += norm(ff(x))
+//   block 1  parallel sublayers under one Dynamic-Tanh pre-norm:            h = dyt(x);  x += mixer(h) + ff(h)
+// Mixers: 0 latent attention (compressed paged cache, shared rotated key part, per-head sink, logistic output gate, optional
+// reuse of an earlier layer's cache); 1 grouped-query attention with biases, rotary embedding from a frequency table, a
+// chunk-local causal mask and a sink, over a paged K/V cache; 2 gated delta rule behind short causal convolutions; 3 xLSTM
+// matrix memory.  Mixers 2 and 3 keep an fp32 state per request in numbered state slots.  Feed-forward: dense SwiGLU or a
+// mixture of experts (softmax or logistic router, relu^2 or gated-SiLU experts).
 //
 // Same structure as the other hosts in this folder: kernels are reached only through the C ABI
 // (include/pegainfer_kernels.h) resolved with dlopen; paging reuses pq::PagePool / pq::KvState; a step is planned and
 // validated first and committed last; one packed metadata block per step is uploaded with a single copy.
 //
 // One entry point runs everything: step() takes a ragged batch -- for each live request its next tokens, whether that
-// is a portion of a prompt or one decoded token -- appends to the cache and returns logits for the rows asked for.
-// Element type of weights / activations / cache is bf16 (tensor-core GEMMs of this library) or float (plain FMA
-// kernels, no reduced-precision matrix mode); softmax, norms, routers and the residual sum are fp32 in both.
+// is a portion of a prompt or one decoded token -- appends to the cache, advances the recurrent state and returns logits
+// for the rows asked for.  Element type of weights / activations / cache is bf16 (tensor-core GEMMs of this library) or
+// float (plain FMA kernels, no reduced-precision matrix mode); softmax, norms, routers, recurrences and the residual sum
+// are fp32 in both.
 #include <dlfcn.h>
 
 #include <algorithm>
@@ -40,34 +46,54 @@ struct LayerCfg {  // mirrored by ctypes in pegainfer_b200/vamadra.py
   int experts, top, groups, keep;
   float route_scale;
   int expert_ff, shared_ff;  // shared_ff 0: no shared expert
+  // mixers 1-3 (mixer_kind 0 = latent attention uses the fields above only)
+  int mixer_kind;            // 0 latent attention, 1 grouped-query attention, 2 gated delta rule, 3 xLSTM matrix memory
+  int kv_heads;              // key/value heads (1, 2); query/key heads of the delta rule
+  int chunk;                 // 1: chunk-local causal mask of this size, 0 = plain causal
+  int conv;                  // 2: taps of the short convolutions
+  int rot_interleaved;       // 1: rotary pairs (2i, 2i+1) instead of (i, i + dims/2)
+  float gate_cap;            // 3: soft cap of the log gates
+  int router_kind;           // 0 softmax scores, best expert per group, renormalised; 1 logistic scores + choice correction, two best per group, plain
+  int expert_act;            // 0 relu^2, 1 gated SiLU
 };
 struct ModelCfg {
   int vocab, width, n_layers;
   float eps;
   int f32, page_size, num_pages, max_requests, device, enable_pdl;
+  int block_kind;  // 0 sequential sublayers, offset RMS norm on their outputs; 1 parallel sublayers under a Dynamic-Tanh pre-norm
+  float embed_scale, logit_scale;
 };
 
 struct Lib {
   void* handle = nullptr;
+  // every design / only the sequential latent-attention block form / only the parallel block form
+#define PV_COMMON(X)                                                                                                                       \
+  X(cuda_set_device) X(cublas_init) X(cublas_destroy) X(gemm_cuda) X(flashinfer_top1_cuda) X(pk_b200_set_pdl) X(pk_b200_launch_count)      \
+  X(pk_res32_skinny_proj) X(pk_convert) X(pk_gemm_strided) X(pk_moe_down_combine) X(pk_moe_grouped_workspace_bytes) X(pk_proj_rows_f32out) \
+  X(pk_scale_to_f32) X(pk_moe_up_act) X(pk_moe_grouped_act)
+#define PV_BLOCK0(X)                                                                                                                        \
+  X(pk_res32_embed) X(pk_res32_offset_norm_add) X(pk_res32_offset_norm_rows) X(pk_act) X(pk_rope_slice) X(pk_latent_kv_append)             \
+  X(pk_latent_attention) X(pk_router_grouped_topk) X(pk_b200_gemv_fused) X(pk_b200_gemm_swiglu)
+#define PV_BLOCK1(X)                                                                                                                        \
+  X(pk_res32_embed_scaled) X(pk_res32_add_dyt) X(pk_res32_dyt_rows) X(pk_gqa_rope_append) X(pk_gqa_attention) X(pk_causal_conv_silu)       \
+  X(pk_gated_delta_seq) X(pk_mlstm_seq) X(pk_head_norm_gate) X(pk_router_topk_ex)
 #define PV_FN(name) decltype(&::name) name = nullptr;
-  PV_FN(cuda_set_device) PV_FN(cublas_init) PV_FN(cublas_destroy) PV_FN(gemm_cuda) PV_FN(flashinfer_top1_cuda) PV_FN(pk_b200_set_pdl)
-  PV_FN(pk_b200_launch_count) PV_FN(pk_res32_embed) PV_FN(pk_res32_offset_norm_add) PV_FN(pk_res32_offset_norm_rows)
-  PV_FN(pk_res32_skinny_proj) PV_FN(pk_act) PV_FN(pk_convert) PV_FN(pk_gemm_strided) PV_FN(pk_rope_slice) PV_FN(pk_latent_kv_append)
-  PV_FN(pk_latent_attention) PV_FN(pk_router_grouped_topk) PV_FN(pk_moe_up_relu2) PV_FN(pk_moe_down_combine)
-  PV_FN(pk_moe_grouped_workspace_bytes) PV_FN(pk_moe_grouped_relu2) PV_FN(pk_proj_rows_f32out) PV_FN(pk_b200_gemv_fused) PV_FN(pk_b200_gemm_swiglu)
+  PV_COMMON(PV_FN) PV_BLOCK0(PV_FN) PV_BLOCK1(PV_FN)
 #undef PV_FN
-  std::string load(const std::string& p) {
+  // a library built for one design need not hold the other block form's kernels: only what `block_kind` runs is required
+  std::string load(const std::string& p, int block_kind) {
     handle = dlopen(p.c_str(), RTLD_NOW | RTLD_LOCAL);
     if (!handle) return std::string("dlopen failed: ") + dlerror();
     std::string missing;
 #define PV_REQ(name)                                             \
   name = reinterpret_cast<decltype(name)>(dlsym(handle, #name)); \
   if (!name) missing += std::string(" ") + #name;
-    PV_REQ(cuda_set_device) PV_REQ(cublas_init) PV_REQ(cublas_destroy) PV_REQ(gemm_cuda) PV_REQ(flashinfer_top1_cuda) PV_REQ(pk_b200_set_pdl)
-    PV_REQ(pk_b200_launch_count) PV_REQ(pk_res32_embed) PV_REQ(pk_res32_offset_norm_add) PV_REQ(pk_res32_offset_norm_rows)
-    PV_REQ(pk_res32_skinny_proj) PV_REQ(pk_act) PV_REQ(pk_convert) PV_REQ(pk_gemm_strided) PV_REQ(pk_rope_slice) PV_REQ(pk_latent_kv_append)
-    PV_REQ(pk_latent_attention) PV_REQ(pk_router_grouped_topk) PV_REQ(pk_moe_up_relu2) PV_REQ(pk_moe_down_combine)
-    PV_REQ(pk_moe_grouped_workspace_bytes) PV_REQ(pk_moe_grouped_relu2) PV_REQ(pk_proj_rows_f32out) PV_REQ(pk_b200_gemv_fused) PV_REQ(pk_b200_gemm_swiglu)
+    PV_COMMON(PV_REQ)
+    if (block_kind == 0) {
+      PV_BLOCK0(PV_REQ)
+    } else {
+      PV_BLOCK1(PV_REQ)
+    }
 #undef PV_REQ
     return missing.empty() ? "" : "kernel library " + p + " lacks:" + missing;
   }
@@ -88,6 +114,11 @@ struct Layer {
   Mat norm1, norm2, q, dkv, dkv_norm, uk, uk_t, uv, sink, g, o;  // mixer; uk_t = W_uk per head as [rank, dim] (made at load)
   Mat gate_up, down;                                       // dense: [gate ; up] stacked
   Mat e_up, e_down, router, s_up, s_down, s_gate;          // experts stacked [experts * ff, width] / [experts * width, ff]
+  // mixers 1-3 / block 1: stacked projections [q | k | v (| gate)], their bias, the few-row fp32 projections [router | za | zb]
+  Mat nb, qkv, qkv_bias, small, conv_w, hnorm;
+  DeviceBuf alpha32, corr32, p0_32, p1_32;                 // float copies of small parameter vectors (made in finalize)
+  Mat alpha, corr, p0, p1;
+  int64_t state_off = 0;                                   // float offset of the layer's block inside a state slot
   DeviceBuf freq;                                          // [rot_dims / 2] fp32 angular frequencies
   float mag = 1.f;
   int owner = -1;       // layer whose cache this layer reads (itself when it owns one)
@@ -102,20 +133,25 @@ struct Model {
   std::string err;
   cudaStream_t st = nullptr;
   int es = 2;  // element size
-  Mat embed, head, final_norm;
-  DeviceBuf cache;
+  Mat embed, head, final_norm, final_b, final_alpha;
+  DeviceBuf final_alpha32;
+  DeviceBuf cache, state;        // paged cache pool; recurrent state, one slot per request id
+  int64_t slot_stride = 0;       // floats per state slot
+  std::vector<char> fresh;       // request slot allocated and not stepped yet: its state is zeroed before the first step
   int64_t page_stride = 0;
   pq::PagePool pool;
   std::vector<pq::KvState> reqs;
   bool finalized = false;
   // per-step scratch, grown to the largest step seen
   int cap_t = 0, cap_r = 0;
+  DeviceBuf h32, big, convo, zs, orec, den;  // block 1: unrounded norm output, stacked projections, conv outputs, few-row fp32, read-out
   DeviceBuf x, xa, q, dkv, qa, gate, olat, ao, mix, gu, act, z, ids, wts, hid, yf, sgl, sh, xr, logits_e, logits_f, logits_bf, sampled_d, top1_val,
       top1_states, trail, moe_ws;
   DeviceBuf meta_d;
   int* meta_h = nullptr;
   size_t meta_cap = 0;
   int* sampled_h = nullptr;
+  int pages_at = 0;  // int offset of the page lists inside the step's metadata block
   bool keep_trail = false;
   int trail_tokens = 0;
   // captured decode steps
@@ -124,6 +160,7 @@ struct Model {
   std::set<GraphKey> seen;
   bool use_graph = true;
   // widest layer
+  int mx_big = 0, mx_conv = 0, mx_small = 0;
   int mx_q = 0, mx_dkv = 0, mx_qa = 0, mx_h = 0, mx_olat = 0, mx_ao = 0, mx_gu = 0, mx_act = 0, mx_e = 0, mx_top = 0, mx_hid = 0;
 
   bool fail(const std::string& m) {
@@ -154,7 +191,11 @@ struct Model {
   bool finalize();
   bool ensure_scratch(int T, int R);
   bool lin(const Mat& W, const void* X, void* Y, int N);
-  bool skinny(const Mat& W, float* out, int T, const char* what);
+  bool skinny(const Mat& W, float* out, int T, const char* what, const float* in32 = nullptr);
+  bool put_rows(Mat& m, int rows, int cols, int row0, int row_step, const void* src, int src_rows, const std::string& name, int got_rows, int got_cols);
+  bool to_f32(const Mat& m, DeviceBuf* out);
+  bool run_experts(Layer& L, int T, const void* shared);
+  bool run_parallel_layer(int li, int T, const int* M, int n);
   bool run_layer(int li, int T, int max_kv, const int* d_pos, const int* d_req, const int* d_poff, const int* d_pages);
   bool forward(int T, int n, int n_rows, int max_kv, int want_sample);
   bool step(int n, const int* tokens, const int* lens, const int* rids, int n_rows, const int* rows, int want_sample);
@@ -172,39 +213,70 @@ bool Model::configure(const ModelCfg& mc, const LayerCfg* lc) {
   c = mc;
   es = c.f32 ? 4 : 2;
   if (c.vocab <= 0 || c.width <= 0 || c.n_layers <= 0) return fail("vocab, width and the number of layers must be positive");
+  if (c.block_kind < 0 || c.block_kind > 1) return fail("unknown block form");
   if (c.page_size <= 0) c.page_size = 16;
   if (c.max_requests <= 0) c.max_requests = 4;
   layers.resize(c.n_layers);
-  int64_t off = 0;
+  int64_t off = 0, soff = 0;
   for (int i = 0; i < c.n_layers; ++i) {
     Layer& L = layers[i];
     L.c = lc[i];
     const LayerCfg& a = L.c;
-    if (a.heads <= 0 || a.dim <= 0 || a.vdim <= 0 || a.kv_rank <= 0 || a.rot_dim < 0) return fail(lname(i, "mixer: sizes must be positive"));
-    if (a.rot_dims < 0 || a.rot_dims > a.rot_dim || (a.rot_dims & 1)) return fail(lname(i, "mixer: rot.dims must be even and at most rot_dim"));
-    if (a.kv_rank > 1024) return fail(lname(i, "mixer: kv_rank above 1024 is outside the attention kernel's range"));
-    if (a.kv_from >= 0) {
-      if (a.kv_from >= i || layers[a.kv_from].c.kv_from >= 0) return fail(lname(i, "mixer: kv_from must name an earlier layer that owns a cache"));
-      const LayerCfg& o = layers[a.kv_from].c;
-      if (o.kv_rank != a.kv_rank || o.rot_dim != a.rot_dim) return fail(lname(i, "mixer: kv_rank / rot_dim differ from the layer it borrows from"));
-      L.owner = a.kv_from;
-      L.cache_off = layers[a.kv_from].cache_off;
+    if (a.mixer_kind < 0 || a.mixer_kind > 3) return fail(lname(i, "mixer: unknown kind"));
+    if ((a.mixer_kind == 0) != (c.block_kind == 0)) return fail(lname(i, "mixer: not available in this block form"));
+    if (a.heads <= 0 || a.dim <= 0 || a.vdim <= 0) return fail(lname(i, "mixer: sizes must be positive"));
+    if (a.mixer_kind == 0) {
+      if (a.kv_rank <= 0 || a.rot_dim < 0) return fail(lname(i, "mixer: sizes must be positive"));
+      if (a.rot_dims < 0 || a.rot_dims > a.rot_dim || (a.rot_dims & 1)) return fail(lname(i, "mixer: rot.dims must be even and at most rot_dim"));
+      if (a.kv_rank > 1024) return fail(lname(i, "mixer: kv_rank above 1024 is outside the attention kernel's range"));
+      if (a.kv_from >= 0) {
+        if (a.kv_from >= i || layers[a.kv_from].c.kv_from >= 0) return fail(lname(i, "mixer: kv_from must name an earlier layer that owns a cache"));
+        const LayerCfg& o = layers[a.kv_from].c;
+        if (o.kv_rank != a.kv_rank || o.rot_dim != a.rot_dim) return fail(lname(i, "mixer: kv_rank / rot_dim differ from the layer it borrows from"));
+        L.owner = a.kv_from;
+        L.cache_off = layers[a.kv_from].cache_off;
+      } else {
+        L.owner = i;
+        L.cache_off = off;
+        off += (int64_t)c.page_size * (a.kv_rank + a.rot_dim);
+      }
+      mx_q = std::max(mx_q, a.heads * (a.dim + a.rot_dim));
+      mx_dkv = std::max(mx_dkv, a.kv_rank + a.rot_dim);
+      mx_qa = std::max(mx_qa, a.heads * (a.kv_rank + a.rot_dim));
+      mx_olat = std::max(mx_olat, a.heads * a.kv_rank);
     } else {
-      L.owner = i;
-      L.cache_off = off;
-      off += (int64_t)c.page_size * (a.kv_rank + a.rot_dim);
+      if (a.kv_heads <= 0 || a.heads % a.kv_heads) return fail(lname(i, "mixer: heads must be a multiple of kv_heads"));
+      if (a.dim > 256 || a.vdim > 256) return fail(lname(i, "mixer: head sizes above 256 are outside the kernels' range"));
+      const int nqk = a.mixer_kind == 1 ? a.heads * a.dim + a.kv_heads * a.dim : 2 * a.kv_heads * a.dim;
+      if (a.mixer_kind == 1) {
+        if (a.rot_dims < 0 || a.rot_dims > a.dim || (a.rot_dims & 1)) return fail(lname(i, "mixer: rot.dims must be even and at most dim"));
+        if (a.chunk < 0) return fail(lname(i, "mixer: mask.size must be positive"));
+        L.owner = i;
+        L.cache_off = off;
+        off += (int64_t)c.page_size * a.kv_heads * (a.dim + a.vdim);
+        off = (off + 7) / 8 * 8;  // every layer's block starts 16-byte aligned in both element types
+        mx_big = std::max(mx_big, nqk + a.kv_heads * a.vdim);
+        mx_q = std::max(mx_q, a.heads * a.dim);
+      } else {
+        if (a.mixer_kind == 2 && a.conv <= 0) return fail(lname(i, "mixer: conv must be positive"));
+        if (a.mixer_kind == 3 && (a.kv_heads != a.heads || !(a.gate_cap > 0.f))) return fail(lname(i, "mixer: inconsistent matrix memory"));
+        L.state_off = soff;
+        soff += (int64_t)a.heads * a.dim * a.vdim;
+        if (a.mixer_kind == 2) soff += (int64_t)std::max(a.conv - 1, 0) * (nqk + a.heads * a.vdim);
+        else soff += (int64_t)a.heads * a.dim + (int64_t)a.heads * (a.vdim + 1);
+        mx_big = std::max(mx_big, nqk + 2 * a.heads * a.vdim);
+        mx_conv = std::max(mx_conv, a.mixer_kind == 2 ? nqk + a.heads * a.vdim : 0);
+      }
+      mx_small = std::max(mx_small, (a.mlp_kind == 2 ? a.experts : 0) + (a.mixer_kind >= 2 ? 2 * a.heads : 0));
     }
     if (a.mlp_kind == 1 && a.ff <= 0) return fail(lname(i, "mlp: ff must be positive"));
+    if (c.block_kind == 1 && a.mlp_kind == 1) return fail(lname(i, "mlp: the parallel block form has no dense feed-forward"));
     if (a.mlp_kind == 2) {
       if (a.experts <= 0 || a.top <= 0 || a.expert_ff <= 0 || a.groups <= 0 || a.experts % a.groups || a.keep <= 0 || a.keep > a.groups ||
           a.top > a.keep * (a.experts / a.groups))
         return fail(lname(i, "mlp: inconsistent router (experts, top, groups)"));
     }
-    mx_q = std::max(mx_q, a.heads * (a.dim + a.rot_dim));
-    mx_dkv = std::max(mx_dkv, a.kv_rank + a.rot_dim);
-    mx_qa = std::max(mx_qa, a.heads * (a.kv_rank + a.rot_dim));
     mx_h = std::max(mx_h, a.heads);
-    mx_olat = std::max(mx_olat, a.heads * a.kv_rank);
     mx_ao = std::max(mx_ao, a.heads * a.vdim);
     if (a.mlp_kind == 1) {
       mx_gu = std::max(mx_gu, 2 * a.ff);
@@ -218,6 +290,7 @@ bool Model::configure(const ModelCfg& mc, const LayerCfg* lc) {
     }
   }
   page_stride = off;
+  slot_stride = soff;
   return true;
 }
 
@@ -236,12 +309,39 @@ bool Model::put(Mat& m, int rows, int cols, int row0, const void* src, int src_r
   return cu(cudaMemcpy((char*)m.d.ptr + (size_t)row0 * cols * es, src, (size_t)src_rows * cols * es, cudaMemcpyDefault), name.c_str());
 }
 
+// the same with destination rows row0, row0 + row_step, ... (interleaving two tensors row by row)
+bool Model::put_rows(Mat& m, int rows, int cols, int row0, int row_step, const void* src, int src_rows, const std::string& name, int got_rows, int got_cols) {
+  if (got_rows != src_rows || got_cols != cols) {
+    char b[256];
+    snprintf(b, sizeof b, "%s: shape [%d, %d] does not match the [%d, %d] the configuration implies", name.c_str(), got_rows, got_cols, src_rows, cols);
+    return fail(b);
+  }
+  if (!m.d.ptr) {
+    m.rows = rows;
+    m.cols = cols;
+    if (!m.d.alloc_zeros((size_t)rows * cols * es)) return fail("allocation failed for " + name);
+  }
+  return cu(cudaMemcpy2D((char*)m.d.ptr + (size_t)row0 * cols * es, (size_t)row_step * cols * es, src, (size_t)cols * es, (size_t)cols * es, src_rows,
+                         cudaMemcpyDefault),
+            name.c_str());
+}
+
+// float copy of a small parameter vector that enters fp32 arithmetic only
+bool Model::to_f32(const Mat& m, DeviceBuf* out) {
+  const long n = (long)m.rows * m.cols;
+  if (!m.d.ptr || n <= 0) return fail("parameter vector missing");
+  if (!out->alloc_zeros((size_t)n * 4)) return fail("allocation failed");
+  return rc(k.pk_convert(m.d.ptr, c.f32, out->ptr, 1, n, st), "parameter conversion");
+}
+
 bool Model::load_tensor(const std::string& name, const void* data, int rows, int cols, int is_f32) {
   if ((is_f32 != 0) != (c.f32 != 0)) return fail(name + ": element type differs from the model's");
   const int W = c.width;
   if (name == "embed") return put(embed, c.vocab, W, 0, data, c.vocab, name, rows, cols);
   if (name == "head") return put(head, c.vocab, W, 0, data, c.vocab, name, rows, cols);
   if (name == "final.norm") return put(final_norm, 1, W, 0, data, 1, name, rows, cols);
+  if (c.block_kind == 1 && name == "final.norm.b") return put(final_b, 1, W, 0, data, 1, name, rows, cols);
+  if (c.block_kind == 1 && name == "final.norm.alpha") return put(final_alpha, 1, 1, 0, data, 1, name, rows, cols);
   if (name.size() < 3 || name[0] != 'l') return fail("unknown tensor " + name);
   const size_t dot = name.find('.');
   if (dot == std::string::npos || dot < 2) return fail("unknown tensor " + name);
@@ -251,6 +351,64 @@ bool Model::load_tensor(const std::string& name, const void* data, int rows, int
   const LayerCfg& a = L.c;
   const std::string sub = name.substr(dot + 1);
   bool ok;
+  if (c.block_kind == 1) {
+    // parallel block: one Dynamic-Tanh norm; projections stacked [q | k | v (| gate)], few-row fp32 projections [router | za | zb]
+    const int H = a.heads, G = a.kv_heads, mk = a.mixer_kind;
+    const int nq = (mk == 2 ? G : H) * a.dim, nk = G * a.dim, nv = (mk == 1 ? G : H) * a.vdim, ng = mk == 1 ? 0 : H * a.vdim;
+    const int nbig = nq + nk + nv + ng, E0 = a.mlp_kind == 2 ? a.experts : 0, nsmall = E0 + (mk >= 2 ? 2 * H : 0);
+    const int taps = a.conv;
+    if (sub == "norm1") ok = put(L.norm1, 1, W, 0, data, 1, name, rows, cols);
+    else if (sub == "norm1.b") ok = put(L.nb, 1, W, 0, data, 1, name, rows, cols);
+    else if (sub == "norm1.alpha") ok = put(L.alpha, 1, 1, 0, data, 1, name, rows, cols);
+    else if (sub == "mix.q") ok = put(L.qkv, nbig, W, 0, data, nq, name, rows, cols);
+    else if (sub == "mix.k") ok = put(L.qkv, nbig, W, nq, data, nk, name, rows, cols);
+    else if (sub == "mix.v") ok = put(L.qkv, nbig, W, nq + nk, data, nv, name, rows, cols);
+    else if (mk >= 2 && sub == "mix.g") ok = put(L.qkv, nbig, W, nq + nk + nv, data, ng, name, rows, cols);
+    else if (sub == "mix.o") ok = put(L.o, W, H * a.vdim, 0, data, W, name, rows, cols);
+    else if (mk == 1 && (sub == "mix.q.b" || sub == "mix.k.b" || sub == "mix.v.b")) {
+      const int n = sub[4] == 'q' ? nq : sub[4] == 'k' ? nk : nv, at = sub[4] == 'q' ? 0 : sub[4] == 'k' ? nq : nq + nk;
+      if (rows != 1 || cols != n) return fail(name + ": shape does not match the configuration");
+      if (!L.qkv_bias.d.ptr) {
+        L.qkv_bias.rows = 1;
+        L.qkv_bias.cols = nbig;
+        if (!L.qkv_bias.d.alloc_zeros((size_t)nbig * es)) return fail("allocation failed for " + name);
+      }
+      ok = cu(cudaMemcpy((char*)L.qkv_bias.d.ptr + (size_t)at * es, data, (size_t)n * es, cudaMemcpyDefault), name.c_str());
+    }
+    else if (mk == 1 && sub == "mix.sink") ok = put(L.sink, 1, H, 0, data, 1, name, rows, cols);
+    else if (mk == 2 && sub == "mix.q.conv") ok = put(L.conv_w, nq + nk + nv, taps, 0, data, nq, name, rows, cols);
+    else if (mk == 2 && sub == "mix.k.conv") ok = put(L.conv_w, nq + nk + nv, taps, nq, data, nk, name, rows, cols);
+    else if (mk == 2 && sub == "mix.v.conv") ok = put(L.conv_w, nq + nk + nv, taps, nq + nk, data, nv, name, rows, cols);
+    else if (mk == 2 && sub == "mix.a") ok = put(L.small, nsmall, W, E0, data, H, name, rows, cols);
+    else if (mk == 2 && sub == "mix.b") ok = put(L.small, nsmall, W, E0 + H, data, H, name, rows, cols);
+    else if (mk == 3 && sub == "mix.f") ok = put(L.small, nsmall, W, E0, data, H, name, rows, cols);
+    else if (mk == 3 && sub == "mix.i") ok = put(L.small, nsmall, W, E0 + H, data, H, name, rows, cols);
+    else if (mk == 2 && sub == "mix.A_log") ok = put(L.p0, 1, H, 0, data, 1, name, rows, cols);
+    else if (mk == 2 && sub == "mix.dt_bias") ok = put(L.p1, 1, H, 0, data, 1, name, rows, cols);
+    else if (mk == 3 && sub == "mix.i.b") ok = put(L.p0, 1, H, 0, data, 1, name, rows, cols);
+    else if (mk == 3 && sub == "mix.f.b") ok = put(L.p1, 1, H, 0, data, 1, name, rows, cols);
+    else if (mk == 2 && sub == "mix.norm") ok = put(L.hnorm, 1, a.vdim, 0, data, 1, name, rows, cols);
+    else if (mk == 3 && sub == "mix.norm") ok = put(L.hnorm, 1, H * a.vdim, 0, data, 1, name, rows, cols);
+    else if (a.mlp_kind == 2 && sub == "mlp.router") ok = put(L.small, nsmall, W, 0, data, a.experts, name, rows, cols);
+    else if (a.mlp_kind == 2 && sub == "mlp.correction") ok = put(L.corr, 1, a.experts, 0, data, 1, name, rows, cols);
+    else if (a.mlp_kind == 2 && sub.rfind("mlp.e", 0) == 0) {
+      const size_t d2 = sub.find('.', 5);
+      if (d2 == std::string::npos) return fail("unknown tensor " + name);
+      const int e = atoi(sub.substr(5, d2 - 5).c_str());
+      const std::string part = sub.substr(d2 + 1);
+      if (e < 0 || e >= a.experts) return fail("expert index out of range: " + name);
+      const int ff = a.expert_ff;
+      if (a.expert_act == 1 && part == "gate") ok = put_rows(L.e_up, a.experts * 2 * ff, W, e * 2 * ff, 2, data, ff, name, rows, cols);
+      else if (a.expert_act == 1 && part == "up") ok = put_rows(L.e_up, a.experts * 2 * ff, W, e * 2 * ff + 1, 2, data, ff, name, rows, cols);
+      else if (a.expert_act == 0 && part == "up") ok = put(L.e_up, a.experts * ff, W, e * ff, data, ff, name, rows, cols);
+      else if (part == "down") ok = put(L.e_down, a.experts * W, ff, e * W, data, W, name, rows, cols);
+      else return fail("unknown tensor " + name);
+    } else {
+      return fail("unknown tensor " + name + " for the configuration of layer " + std::to_string(li));
+    }
+    if (ok) L.got.insert(sub);
+    return ok;
+  }
   if (sub == "norm1") ok = put(L.norm1, 1, W, 0, data, 1, name, rows, cols);
   else if (sub == "norm2") ok = put(L.norm2, 1, W, 0, data, 1, name, rows, cols);
   else if (sub == "mix.q") ok = put(L.q, a.heads * (a.dim + a.rot_dim), W, 0, data, a.heads * (a.dim + a.rot_dim), name, rows, cols);
@@ -321,16 +479,29 @@ static void rotary_table(const LayerCfg& a, std::vector<float>* f, float* mag) {
 
 bool Model::finalize() {
   if (!embed.d.ptr || !head.d.ptr || !final_norm.d.ptr) return fail("embed / head / final.norm missing");
+  if (c.block_kind == 1 && (!final_b.d.ptr || !final_alpha.d.ptr || !to_f32(final_alpha, &final_alpha32))) return fail("final.norm.b / final.norm.alpha missing");
+  if (slot_stride > 0 && !state.alloc_zeros((size_t)c.max_requests * slot_stride * 4)) return fail("state slot allocation failed");
+  if (page_stride == 0) page_stride = 8;  // no layer keeps a paged cache: the pool only counts tokens
   for (int i = 0; i < c.n_layers; ++i) {
     Layer& L = layers[i];
     const LayerCfg& a = L.c;
-    std::vector<std::string> need = {"norm1", "mix.q", "mix.uk", "mix.uv", "mix.sink", "mix.g", "mix.o"};
-    if (a.kv_from < 0) need.insert(need.end(), {"mix.dkv", "mix.dkv.norm"});
-    if (a.mlp_kind) need.push_back("norm2");
+    std::vector<std::string> need;
+    if (c.block_kind == 0) {
+      need = {"norm1", "mix.q", "mix.uk", "mix.uv", "mix.sink", "mix.g", "mix.o"};
+      if (a.kv_from < 0) need.insert(need.end(), {"mix.dkv", "mix.dkv.norm"});
+      if (a.mlp_kind) need.push_back("norm2");
+    } else {
+      need = {"norm1", "norm1.b", "norm1.alpha", "mix.q", "mix.k", "mix.v", "mix.o"};
+      if (a.mixer_kind == 1) need.insert(need.end(), {"mix.q.b", "mix.k.b", "mix.v.b", "mix.sink"});
+      if (a.mixer_kind == 2) need.insert(need.end(), {"mix.q.conv", "mix.k.conv", "mix.v.conv", "mix.a", "mix.b", "mix.A_log", "mix.dt_bias", "mix.norm", "mix.g"});
+      if (a.mixer_kind == 3) need.insert(need.end(), {"mix.i", "mix.f", "mix.i.b", "mix.f.b", "mix.norm", "mix.g"});
+      if (a.mlp_kind == 2) need.push_back("mlp.correction");
+    }
     if (a.mlp_kind == 1) need.insert(need.end(), {"mlp.gate", "mlp.up", "mlp.down"});
     if (a.mlp_kind == 2) {
       need.push_back("mlp.router");
       for (int e = 0; e < a.experts; ++e) {
+        if (a.expert_act == 1) need.push_back("mlp.e" + std::to_string(e) + ".gate");
         need.push_back("mlp.e" + std::to_string(e) + ".up");
         need.push_back("mlp.e" + std::to_string(e) + ".down");
       }
@@ -338,6 +509,12 @@ bool Model::finalize() {
     }
     for (auto& n : need)
       if (!L.got.count(n)) return fail("tensor " + lname(i, n.c_str()) + " is missing");
+    if (c.block_kind == 1) {
+      if (!to_f32(L.alpha, &L.alpha32)) return false;
+      if (a.mlp_kind == 2 && !to_f32(L.corr, &L.corr32)) return false;
+      if (a.mixer_kind >= 2 && (!to_f32(L.p0, &L.p0_32) || !to_f32(L.p1, &L.p1_32))) return false;
+      if (a.mixer_kind != 1) continue;  // only attention rotates
+    }
     std::vector<float> f;
     rotary_table(a, &f, &L.mag);
     if (!L.freq.alloc_zeros(f.size() * 4) || !cu(cudaMemcpy(L.freq.ptr, f.data(), f.size() * 4, cudaMemcpyHostToDevice), "rotary table"))
@@ -354,6 +531,7 @@ bool Model::finalize() {
   std::vector<int> pad;
   pool.acquire(1, &pad);
   reqs.assign(c.max_requests, pq::KvState());
+  fresh.assign(c.max_requests, 0);
   if (cudaMallocHost((void**)&sampled_h, 4096) != cudaSuccess) return fail("pinned allocation failed");
   if (!top1_val.alloc_zeros(64) || !top1_states.alloc_zeros(1 << 16)) return fail("sampler scratch allocation failed");
   finalized = true;
@@ -372,6 +550,9 @@ bool Model::ensure_scratch(int T, int R) {
          act.alloc_uninit(n * std::max(mx_act, 1) * es) && z.alloc_uninit(n * std::max(mx_e, 1) * 4) && ids.alloc_uninit(n * std::max(mx_top, 1) * 4) &&
          wts.alloc_uninit(n * std::max(mx_top, 1) * 4) && hid.alloc_uninit(n * std::max(mx_hid, 1) * es) && yf.alloc_uninit(n * W * 4) &&
          sgl.alloc_uninit(n * 4) && sh.alloc_uninit(n * W * es);
+    if (ok && c.block_kind == 1)
+      ok = h32.alloc_uninit(n * W * 4) && big.alloc_uninit(n * std::max(mx_big, 1) * es) && convo.alloc_uninit(n * std::max(mx_conv, 1) * es) &&
+           zs.alloc_uninit(n * std::max(mx_small, 1) * 4) && orec.alloc_uninit(n * std::max(mx_ao, 1) * 4) && den.alloc_uninit(n * std::max(mx_h, 1) * 4);
     if (ok && !c.f32 && (int)n >= kGroupedMinTokens) {  // bucketed experts for prompt portions
       long ws = 0;
       for (auto& L : layers)
@@ -401,12 +582,13 @@ bool Model::lin(const Mat& W, const void* X, void* Y, int N) {
 
 // out[T, W.rows] (fp32) = residual W^T for the few-row projections (gates, router): from the fp32 residual per token, or -- for
 // a prompt portion in bf16 -- from its bf16 copy on the tensor cores (fp32 accumulation and output either way)
-bool Model::skinny(const Mat& W, float* out, int T, const char* what) {
+bool Model::skinny(const Mat& W, float* out, int T, const char* what, const float* in32) {
+  if (!in32) in32 = (const float*)x.ptr;
   if (!c.f32 && T >= kGroupedMinTokens) {
     const int r = k.pk_proj_rows_f32out(W.d.ptr, xa.ptr, out, W.rows, W.cols, T, st);
     if (r != -2) return rc(r, what);
   }
-  return rc(k.pk_res32_skinny_proj(W.d.ptr, (const float*)x.ptr, out, W.rows, W.cols, T, c.f32, st), what);
+  return rc(k.pk_res32_skinny_proj(W.d.ptr, in32, out, W.rows, W.cols, T, c.f32, st), what);
 }
 
 bool Model::run_layer(int li, int T, int max_kv, const int* d_pos, const int* d_req, const int* d_poff, const int* d_pages) {
@@ -481,20 +663,7 @@ bool Model::run_layer(int li, int T, int max_kv, const int* d_pos, const int* d_
       if (!skinny(L.s_gate, (float*)sgl.ptr, T, "shared expert gate")) return false;
       shared = sh.ptr;
     }
-    // many tokens: rows bucketed by expert on the tensor cores; a few tokens: per token, reading only the chosen experts' weights
-    int grouped = -2;
-    if (!f32 && T >= kGroupedMinTokens && moe_ws.ptr) {
-      grouped = k.pk_moe_grouped_relu2(xa.ptr, L.e_up.d.ptr, L.e_down.d.ptr, (const int*)ids.ptr, (const float*)wts.ptr, shared, (const float*)sgl.ptr,
-                                       (float*)yf.ptr, moe_ws.ptr, T, a.top, a.experts, W, a.expert_ff, st);
-      if (grouped != -2 && !rc(grouped, "experts (grouped)")) return false;
-    }
-    if (grouped == -2 && !rc(k.pk_moe_up_relu2(xa.ptr, L.e_up.d.ptr, (const int*)ids.ptr, hid.ptr, T, a.top, W, a.expert_ff, f32, st), "experts up"))
-      return false;
-    if (grouped == -2 &&
-        !rc(k.pk_moe_down_combine(hid.ptr, L.e_down.d.ptr, (const int*)ids.ptr, (const float*)wts.ptr, shared, (const float*)sgl.ptr, (float*)yf.ptr, T,
-                                  a.top, W, a.expert_ff, f32, st),
-            "experts down"))
-      return false;
+    if (!run_experts(L, T, shared)) return false;
     if (!rc(k.pk_res32_offset_norm_add(yf.ptr, 1, L.norm2.d.ptr, (float*)x.ptr, xa.ptr, W, T, c.eps, f32, st), "norm2")) return false;
   }
   if (keep_trail)
@@ -502,22 +671,125 @@ bool Model::run_layer(int li, int T, int max_kv, const int* d_pos, const int* d_
   return true;
 }
 
+// routed experts of one layer for the tokens in xa: router logits are in zs (block 1) or z (block 0); result in yf (fp32)
+bool Model::run_experts(Layer& L, int T, const void* shared) {
+  const LayerCfg& a = L.c;
+  const int W = c.width, f32 = c.f32;
+  // many tokens: rows bucketed by expert on the tensor cores; a few tokens: per token, reading only the chosen experts' weights
+  int grouped = -2;
+  if (!f32 && T >= kGroupedMinTokens && moe_ws.ptr) {
+    grouped = k.pk_moe_grouped_act(xa.ptr, L.e_up.d.ptr, L.e_down.d.ptr, (const int*)ids.ptr, (const float*)wts.ptr, shared, (const float*)sgl.ptr,
+                                   (float*)yf.ptr, moe_ws.ptr, T, a.top, a.experts, W, a.expert_ff, a.expert_act, st);
+    if (grouped != -2 && !rc(grouped, "experts (grouped)")) return false;
+  }
+  if (grouped == -2 && !rc(k.pk_moe_up_act(xa.ptr, L.e_up.d.ptr, (const int*)ids.ptr, hid.ptr, T, a.top, W, a.expert_ff, a.expert_act, f32, st), "experts up"))
+    return false;
+  if (grouped == -2 &&
+      !rc(k.pk_moe_down_combine(hid.ptr, L.e_down.d.ptr, (const int*)ids.ptr, (const float*)wts.ptr, shared, (const float*)sgl.ptr, (float*)yf.ptr, T,
+                                a.top, W, a.expert_ff, f32, st),
+          "experts down"))
+    return false;
+  return true;
+}
+
+// Parallel block: on entry xa / h32 hold dyt(x) of this layer; on exit mix (element type) and, with a feed-forward, yf (fp32) hold the
+// two sublayers' outputs -- the caller adds them to the residual together with the next norm.
+bool Model::run_parallel_layer(int li, int T, const int* M, int n) {
+  Layer& L = layers[li];
+  const LayerCfg& a = L.c;
+  const int f32 = c.f32, H = a.heads, G = a.kv_heads, mk = a.mixer_kind;
+  const int *d_pos = M + T, *d_req = M + 2 * T, *d_poff = M + 3 * T, *d_slot = M + 3 * T + n, *d_row0 = M + 3 * T + 2 * n, *d_len = M + 3 * T + 3 * n;
+  const int* d_pages = M + pages_at;
+  const int nq = (mk == 2 ? G : H) * a.dim, nk = G * a.dim, nv = (mk == 1 ? G : H) * a.vdim, ng = mk == 1 ? 0 : H * a.vdim;
+  const int nbig = nq + nk + nv + ng, E0 = a.mlp_kind == 2 ? a.experts : 0, nsmall = E0 + (mk >= 2 ? 2 * H : 0);
+  if (!lin(L.qkv, xa.ptr, big.ptr, T)) return false;
+  if (nsmall > 0 && !skinny(L.small, (float*)zs.ptr, T, "few-row projections", (const float*)h32.ptr)) return false;
+  float* slot0 = state.ptr ? (float*)state.ptr + L.state_off : nullptr;
+  if (mk == 1) {
+    char* pool_base = (char*)cache.ptr + (size_t)L.cache_off * es;
+    if (!rc(k.pk_gqa_rope_append(big.ptr, nbig, L.qkv_bias.d.ptr, d_pos, d_req, d_poff, d_pages, q.ptr, pool_base, page_stride, c.page_size, H, G, a.dim,
+                                 a.vdim, a.rot_dims, a.rot_interleaved, (const float*)L.freq.ptr, L.mag, T, f32, st),
+            "rotation + cache append"))
+      return false;
+    if (!rc(k.pk_gqa_attention(q.ptr, pool_base, L.sink.d.ptr, d_pos, d_req, d_poff, d_pages, ao.ptr, page_stride, c.page_size, T, H, G, a.dim, a.vdim,
+                               a.scale, a.chunk, f32, st),
+            "attention"))
+      return false;
+  } else if (mk == 2) {
+    const int C = nq + nk + nv;
+    if (!rc(k.pk_causal_conv_silu(big.ptr, nbig, L.conv_w.d.ptr, slot0 + (size_t)H * a.dim * a.vdim, slot_stride, d_req, d_slot, d_row0, d_len, convo.ptr, C, C,
+                                  a.conv, T, n, f32, st),
+            "short convolution"))
+      return false;
+    if (!rc(k.pk_gated_delta_seq(convo.ptr, C, 0, nq, nq + nk, (const float*)zs.ptr, nsmall, E0, E0 + H, (const float*)L.p0_32.ptr, (const float*)L.p1_32.ptr,
+                                 slot0, slot_stride, d_slot, d_row0, d_len, (float*)orec.ptr, H, G, a.dim, a.vdim, n, f32, st),
+            "gated delta rule"))
+      return false;
+    if (!rc(k.pk_head_norm_gate((const float*)orec.ptr, nullptr, L.hnorm.d.ptr, 0, big.ptr, nbig, nq + nk + nv, ao.ptr, T, H, a.vdim, c.eps, 0, f32, st),
+            "read-out norm"))
+      return false;
+  } else {
+    if (!rc(k.pk_mlstm_seq(big.ptr, nbig, 0, nq, nq + nk, (const float*)zs.ptr, nsmall, E0, E0 + H, (const float*)L.p0_32.ptr, (const float*)L.p1_32.ptr,
+                           a.gate_cap, slot0, slot_stride, d_slot, d_row0, d_len, (float*)orec.ptr, (float*)den.ptr, H, a.dim, a.vdim, n, f32, st),
+            "matrix memory"))
+      return false;
+    if (!rc(k.pk_head_norm_gate((const float*)orec.ptr, (const float*)den.ptr, L.hnorm.d.ptr, a.vdim, big.ptr, nbig, nq + nk + nv, ao.ptr, T, H, a.vdim,
+                                c.eps, 1, f32, st),
+            "read-out norm"))
+      return false;
+  }
+  if (!lin(L.o, ao.ptr, mix.ptr, T)) return false;
+  if (a.mlp_kind == 2) {
+    if (!rc(k.pk_router_topk_ex((const float*)zs.ptr, nsmall, (const float*)L.corr32.ptr, (int*)ids.ptr, (float*)wts.ptr, T, a.experts, a.top, a.groups,
+                                a.keep, a.route_scale, a.router_kind, a.router_kind == 1 ? 2 : 1, a.router_kind == 1 ? 0 : 1, st),
+            "router top-k"))
+      return false;
+    if (!run_experts(L, T, nullptr)) return false;
+  }
+  return true;
+}
+
 // everything between the metadata upload and the final synchronisation: launches only (no allocation, no synchronisation)
 bool Model::forward(int T, int n, int n_rows, int max_kv, int want_sample) {
   const int* M = meta_d.i32();
-  const int *d_tok = M, *d_pos = M + T, *d_req = M + 2 * T, *d_poff = M + 3 * T, *d_rows = M + 3 * T + n, *d_pages = M + 3 * T + n + n_rows;
-  if (!rc(k.pk_res32_embed(embed.d.ptr, d_tok, (float*)x.ptr, xa.ptr, c.width, T, c.f32, st), "embedding")) return false;
-  for (int li = 0; li < c.n_layers; ++li)
-    if (!run_layer(li, T, max_kv, d_pos, d_req, d_poff, d_pages)) return false;
+  const int *d_tok = M, *d_pos = M + T, *d_req = M + 2 * T, *d_poff = M + 3 * T, *d_rows = M + 3 * T + 4 * n, *d_pages = M + 3 * T + 4 * n + n_rows;
+  pages_at = 3 * T + 4 * n + n_rows;
+  const int W = c.width;
+  if (c.block_kind == 0) {
+    if (!rc(k.pk_res32_embed(embed.d.ptr, d_tok, (float*)x.ptr, xa.ptr, W, T, c.f32, st), "embedding")) return false;
+    for (int li = 0; li < c.n_layers; ++li)
+      if (!run_layer(li, T, max_kv, d_pos, d_req, d_poff, d_pages)) return false;
+  } else {
+    if (!rc(k.pk_res32_embed_scaled(embed.d.ptr, d_tok, (float*)x.ptr, W, T, c.embed_scale, c.f32, st), "embedding")) return false;
+    // every layer's residual sum is folded into the next layer's norm (the last one into a plain sum)
+    for (int li = 0; li <= c.n_layers; ++li) {
+      const Layer* P = li > 0 ? &layers[li - 1] : nullptr;
+      const Layer* N = li < c.n_layers ? &layers[li] : nullptr;
+      if (!rc(k.pk_res32_add_dyt(P ? mix.ptr : nullptr, P && P->c.mlp_kind == 2 ? (const float*)yf.ptr : nullptr, N ? (const float*)N->alpha32.ptr : nullptr,
+                                 N ? N->norm1.d.ptr : nullptr, N ? N->nb.d.ptr : nullptr, (float*)x.ptr, xa.ptr, (float*)h32.ptr, W, T, c.f32, st),
+              "residual sum + norm"))
+        return false;
+      if (keep_trail && P &&
+          !cu(cudaMemcpyAsync((char*)trail.ptr + (size_t)(li - 1) * T * W * 4, x.ptr, (size_t)T * W * 4, cudaMemcpyDeviceToDevice, st), "trail copy"))
+        return false;
+      if (N && !run_parallel_layer(li, T, M, n)) return false;
+    }
+  }
   if (n_rows > 0) {
-    if (!rc(k.pk_res32_offset_norm_rows((const float*)x.ptr, d_rows, final_norm.d.ptr, xr.ptr, c.width, n_rows, c.eps, c.f32, st), "final norm"))
+    if (c.block_kind == 0) {
+      if (!rc(k.pk_res32_offset_norm_rows((const float*)x.ptr, d_rows, final_norm.d.ptr, xr.ptr, W, n_rows, c.eps, c.f32, st), "final norm")) return false;
+    } else if (!rc(k.pk_res32_dyt_rows((const float*)x.ptr, d_rows, (const float*)final_alpha32.ptr, final_norm.d.ptr, final_b.d.ptr, xr.ptr, W, n_rows, c.f32,
+                                       st),
+                   "final norm")) {
       return false;
+    }
     if (!lin(head, xr.ptr, logits_e.ptr, n_rows)) return false;
-    if (!rc(k.pk_convert(logits_e.ptr, c.f32, logits_f.ptr, 1, (long)n_rows * c.vocab, st), "logits")) return false;
+    const float ls = c.block_kind == 1 ? c.logit_scale : 1.f;
+    if (!rc(k.pk_scale_to_f32(logits_e.ptr, c.f32, (float*)logits_f.ptr, (long)n_rows * c.vocab, ls, st), "logits")) return false;
     if (want_sample) {
       const pk_bf16* lb = (const pk_bf16*)logits_e.ptr;
-      if (c.f32) {
-        if (!rc(k.pk_convert(logits_e.ptr, 1, logits_bf.ptr, 0, (long)n_rows * c.vocab, st), "logits")) return false;
+      if (c.f32 || ls != 1.f) {  // the sampler reads bf16 rows of the final (scaled) logits
+        if (!rc(k.pk_convert(logits_f.ptr, 1, logits_bf.ptr, 0, (long)n_rows * c.vocab, st), "logits")) return false;
         lb = (const pk_bf16*)logits_bf.ptr;
       }
       for (int i = 0; i < n_rows; ++i)
@@ -571,8 +843,8 @@ bool Model::step(int n, const int* tokens, const int* lens, const int* rids, int
       }
     }
   } txn{this, {}, false};
-  // metadata block: [tok T][pos T][req T][page_off n][rows R][pages ...]
-  std::vector<int> meta((size_t)3 * T + n + n_rows);
+  // metadata block: [tok T][pos T][req T][page_off n][slot n][row0 n][len n][rows R][pages ...]
+  std::vector<int> meta((size_t)3 * T + 4 * n + n_rows);
   int t0 = 0, max_kv = 0;
   std::vector<int> page_list;
   for (int i = 0; i < n; ++i) {
@@ -586,12 +858,19 @@ bool Model::step(int n, const int* tokens, const int* lens, const int* rids, int
       meta[2 * T + t0 + t] = i;
     }
     meta[3 * T + i] = (int)page_list.size();
+    meta[3 * T + n + i] = rids[i];
+    meta[3 * T + 2 * n + i] = t0;
+    meta[3 * T + 3 * n + i] = lens[i];
+    if (fresh[rids[i]] && state.ptr) {  // a slot that another request used before: its state starts at zero
+      if (!cu(cudaMemsetAsync((float*)state.ptr + (size_t)rids[i] * slot_stride, 0, (size_t)slot_stride * 4, st), "state reset")) return false;
+    }
+    fresh[rids[i]] = 0;
     page_list.insert(page_list.end(), s.pages.begin(), s.pages.end());
     s.seq_len += lens[i];
     max_kv = std::max(max_kv, s.seq_len);
     t0 += lens[i];
   }
-  for (int i = 0; i < n_rows; ++i) meta[3 * T + n + i] = rows[i];
+  for (int i = 0; i < n_rows; ++i) meta[3 * T + 4 * n + i] = rows[i];
   meta.insert(meta.end(), page_list.begin(), page_list.end());
   if (meta.size() > meta_cap) {
     cudaStreamSynchronize(st);
@@ -662,7 +941,7 @@ PV_API void* pv_create(const pv::ModelCfg* mc, const pv::LayerCfg* lc, const cha
     return nullptr;
   };
   if (!m->configure(*mc, lc)) return bail(m->err);
-  std::string e = m->k.load(kernel_lib_path);
+  std::string e = m->k.load(kernel_lib_path, mc->block_kind);
   if (!e.empty()) return bail(e);
   if (m->k.cuda_set_device(mc->device) != 0) return bail("cuda_set_device failed (no CUDA device?)");
   if (cudaStreamCreateWithFlags(&m->st, cudaStreamNonBlocking) != cudaSuccess)
@@ -684,6 +963,7 @@ PV_API int pv_request_alloc(void* mp) {
     if (!v[i].live) {
       v[i] = pq::KvState();
       v[i].live = true;
+      PV_M->fresh[i] = 1;
       return (int)i;
     }
   PV_M->err = "every request slot is in use";

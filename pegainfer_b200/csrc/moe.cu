@@ -5,6 +5,10 @@
 //           scores as its best expert, only the `keep` best groups stay eligible; the `top` best eligible experts are
 //           chosen (lowest index wins ties); weight = s / (sum of chosen s + 1e-20) * scale.
 //   experts: hid[t,k,:] = act(W_up[e_k] x_t);  y[t] = sum_k w_k W_down[e_k] hid[t,k,:]  (+ logistic(g_t) * shared[t]).
+//   Variants (parameters of the `_ex` / `_act` entry points): logistic scores instead of softmax, a per-expert correction added to
+//   the scores for the CHOICE only (weights use the uncorrected score), a group scoring as the sum of its two best corrected
+//   scores, weights not renormalised; experts with a gated activation, hid = silu(W_gate x) * (W_up x), whose gate and up rows
+//   are stored interleaved (row 2f = gate f, row 2f + 1 = up f) so that one pass yields both.
 // The per-token form reads only the chosen experts' weights: the decode path (a few tokens) is bound by those bytes.
 #include "common.cuh"
 #include "typed.cuh"
@@ -25,79 +29,97 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 }
 
 // one warp per token; shared memory: scores [E] + group eligibility [groups]
-__global__ void router_grouped_topk_kernel(const float* __restrict__ z, int* __restrict__ ids, float* __restrict__ wts, int E, int top,
-                                           int groups, int keep, float scale) {
+// score_kind 0: softmax over the experts, 1: logistic per expert.  corr (may be null): added to the score for choosing.
+// group_top 1: a group scores as its best expert, 2: as the sum of its two best.  renorm 1: weights divided by their sum.
+__global__ void router_grouped_topk_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ corr, int* __restrict__ ids,
+                                           float* __restrict__ wts, int E, int top, int groups, int keep, float scale, int score_kind, int group_top,
+                                           int renorm) {
   extern __shared__ float sm[];
   pdl_wait();
   pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   const int t = blockIdx.x, lane = threadIdx.x;
-  float* s = sm;            // [E]
-  float* gs = s + E;        // [groups] group score, -1 once taken
+  float* s = sm;            // [E] score (weight source)
+  float* c = s + E;         // [E] choice score = score + correction; -inf once taken
+  float* gs = c + E;        // [groups] group score, -inf once taken
   float* ok = gs + groups;  // [groups] 1 = eligible
-  const float* zr = z + (size_t)t * E;
-  float mx = -INFINITY;
-  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, zr[e]);
-  mx = warp_max(mx);
-  float sum = 0.f;
-  for (int e = lane; e < E; e += 32) {
-    const float v = expf(zr[e] - mx);
-    s[e] = v;
-    sum += v;
+  const float* zr = z + (size_t)t * ldz;
+  if (score_kind == 0) {
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, zr[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+      const float v = expf(zr[e] - mx);
+      s[e] = v;
+      sum += v;
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.f / sum;
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) s[e] *= inv;
+  } else {
+    for (int e = lane; e < E; e += 32) s[e] = 1.f / (1.f + expf(-zr[e]));
   }
-  sum = warp_sum(sum);
-  const float inv = 1.f / sum;
   __syncwarp();
-  for (int e = lane; e < E; e += 32) s[e] *= inv;
+  for (int e = lane; e < E; e += 32) c[e] = s[e] + (corr ? corr[e] : 0.f);
   __syncwarp();
   const int per = E / groups;
   for (int g = lane; g < groups; g += 32) {
-    float b = -1.f;
-    for (int e = 0; e < per; ++e) b = fmaxf(b, s[g * per + e]);
-    gs[g] = b;
+    float b1 = -INFINITY, b2 = -INFINITY;
+    for (int e = 0; e < per; ++e) {
+      const float v = c[g * per + e];
+      if (v > b1) {
+        b2 = b1;
+        b1 = v;
+      } else if (v > b2) {
+        b2 = v;
+      }
+    }
+    gs[g] = (group_top >= 2 && per >= 2) ? b1 + b2 : b1;
     ok[g] = 0.f;
   }
   __syncwarp();
   for (int r = 0; r < keep; ++r) {
-    float bv = -2.f;
+    float bv = -INFINITY;
     int bi = 0x7fffffff;
     for (int g = lane; g < groups; g += 32)
-      if (gs[g] > bv) {
+      if (ok[g] == 0.f && (gs[g] > bv || bi == 0x7fffffff)) {
         bv = gs[g];
         bi = g;
       }
     warp_argmax(bv, bi);
-    if (lane == 0) {
-      gs[bi] = -3.f;
-      ok[bi] = 1.f;
-    }
+    if (lane == 0) ok[bi] = 1.f;
     __syncwarp();
   }
   float total = 0.f;
   for (int r = 0; r < top; ++r) {
-    float bv = -2.f;
+    float bv = -INFINITY;
     int bi = 0x7fffffff;
     for (int e = lane; e < E; e += 32)
-      if (ok[e / per] > 0.f && s[e] > bv) {
-        bv = s[e];
+      if (ok[e / per] > 0.f && c[e] != -INFINITY && (c[e] > bv || bi == 0x7fffffff)) {
+        bv = c[e];
         bi = e;
       }
     warp_argmax(bv, bi);
-    total += bv;
+    const float w = s[bi];
+    total += w;
     if (lane == 0) {
       ids[(size_t)t * top + r] = bi;
-      wts[(size_t)t * top + r] = bv;
-      s[bi] = -4.f;  // taken
+      wts[(size_t)t * top + r] = w;
+      c[bi] = -INFINITY;  // taken
     }
     __syncwarp();
   }
-  for (int r = lane; r < top; r += 32) wts[(size_t)t * top + r] = wts[(size_t)t * top + r] / (total + 1e-20f) * scale;
+  const float f = renorm ? scale / (total + 1e-20f) : scale;
+  for (int r = lane; r < top; r += 32) wts[(size_t)t * top + r] *= f;
 }
 
 constexpr int kMoeDownRowsPerBlock = 8;  // one output row per warp: each row already streams `top` weight rows
 constexpr int kMoeRowsPerBlock = 32;  // weight rows per CTA: a decode step spreads one expert over many SMs
 
-// hid[t, k, f] = act(W_up[ids[t,k]][f] . x[t]); act = relu^2.  Grid (token, choice, slice of ff rows).
-template <typename E>
+// hid[t, k, f] = act(W_up[ids[t,k]][f] . x[t]).  GATED 0: act = relu^2, W_up [experts, ff, width].  GATED 1: W_up [experts, 2 ff, width] with
+// row 2f = gate f and row 2f + 1 = up f; hid = silu(gate . x) * (up . x).  Grid (token, choice, slice of ff rows).
+template <typename E, int GATED>
 __global__ void moe_up_kernel(const E* __restrict__ xa, const E* __restrict__ w_up, const int* __restrict__ ids, E* __restrict__ hid, int width,
                               int ff) {
   extern __shared__ __align__(16) float xs[];
@@ -107,14 +129,18 @@ __global__ void moe_up_kernel(const E* __restrict__ xa, const E* __restrict__ w_
   const int tok = blockIdx.x, k = blockIdx.y, top = gridDim.y;
   for (int i = threadIdx.x; i < width; i += blockDim.x) xs[i] = to_f(xa[(size_t)tok * width + i]);
   __syncthreads();
-  const E* W = w_up + (size_t)ids[(size_t)tok * top + k] * ff * width;
+  const E* W = w_up + (size_t)ids[(size_t)tok * top + k] * ff * width * (GATED ? 2 : 1);
   const int f_end = min(ff, (int)(blockIdx.z + 1) * kMoeRowsPerBlock);
   for (int f = blockIdx.z * kMoeRowsPerBlock + warp; f < f_end; f += nw) {
-    const float acc = warp_dot(W + (size_t)f * width, xs, width, lane);
-    if (lane == 0) {
-      const float u = fmaxf(acc, 0.f);
-      hid[((size_t)tok * top + k) * ff + f] = from_f<E>(u * u);
+    float r;
+    if (GATED) {
+      const float g = warp_dot(W + (size_t)(2 * f) * width, xs, width, lane), u = warp_dot(W + (size_t)(2 * f + 1) * width, xs, width, lane);
+      r = g / (1.f + expf(-g)) * u;
+    } else {
+      const float u = fmaxf(warp_dot(W + (size_t)f * width, xs, width, lane), 0.f);
+      r = u * u;
     }
+    if (lane == 0) hid[((size_t)tok * top + k) * ff + f] = from_f<E>(r);
   }
 }
 
@@ -146,25 +172,38 @@ __global__ void moe_down_kernel(const E* __restrict__ hid, const E* __restrict__
 
 using namespace pk;
 
+extern "C" int pk_router_topk_ex(const float* logits, int ld, const float* correction, int* ids, float* weights, int tokens, int experts, int top,
+                                int groups, int keep, float scale, int score_kind, int group_top, int renorm, pk_stream st) {
+  if (!logits || !ids || !weights || tokens <= 0 || experts <= 0 || top <= 0 || groups <= 0 || experts % groups || keep <= 0 || keep > groups ||
+      top > keep * (experts / groups) || ld < experts || score_kind < 0 || score_kind > 1 || group_top < 1 || group_top > 2)
+    return -1;
+  launch(router_grouped_topk_kernel, dim3(tokens), dim3(32), (size_t)(2 * experts + 2 * groups) * sizeof(float), st, true, logits, ld, correction, ids,
+         weights, experts, top, groups, keep, scale, score_kind, group_top, renorm);
+  return (int)cudaGetLastError();
+}
+
 extern "C" int pk_router_grouped_topk(const float* logits, int* ids, float* weights, int tokens, int experts, int top, int groups, int keep,
                                       float scale, pk_stream st) {
-  if (!logits || !ids || !weights || tokens <= 0 || experts <= 0 || top <= 0 || groups <= 0 || experts % groups || keep <= 0 ||
-      keep > groups || top > keep * (experts / groups))
-    return -1;
-  launch(router_grouped_topk_kernel, dim3(tokens), dim3(32), (size_t)(experts + 2 * groups) * sizeof(float), st, true, logits, ids, weights, experts,
-         top, groups, keep, scale);
+  return pk_router_topk_ex(logits, experts, nullptr, ids, weights, tokens, experts, top, groups, keep, scale, 0, 1, 1, st);
+}
+
+extern "C" int pk_moe_up_act(const void* xa, const void* w_up, const int* ids, void* hid, int tokens, int top, int width, int ff, int act, int f32,
+                             pk_stream st) {
+  if (!xa || !w_up || !ids || !hid || tokens <= 0 || top <= 0 || width <= 0 || ff <= 0 || act < 0 || act > 1) return -1;
+  const size_t smem = (size_t)width * sizeof(float);
+  const dim3 grid(tokens, top, (ff + kMoeRowsPerBlock - 1) / kMoeRowsPerBlock);
+#define PK_UP(E, G) launch(moe_up_kernel<E, G>, grid, dim3(256), smem, st, true, (const E*)xa, (const E*)w_up, ids, (E*)hid, width, ff)
+  if (f32 && act) PK_UP(float, 1);
+  else if (f32) PK_UP(float, 0);
+  else if (act) PK_UP(bf16, 1);
+  else PK_UP(bf16, 0);
+#undef PK_UP
   return (int)cudaGetLastError();
 }
 
 extern "C" int pk_moe_up_relu2(const void* xa, const void* w_up, const int* ids, void* hid, int tokens, int top, int width, int ff, int f32,
                                pk_stream st) {
-  if (!xa || !w_up || !ids || !hid || tokens <= 0 || top <= 0 || width <= 0 || ff <= 0) return -1;
-  const size_t smem = (size_t)width * sizeof(float);
-  if (f32)
-    launch(moe_up_kernel<float>, dim3(tokens, top, (ff + kMoeRowsPerBlock - 1) / kMoeRowsPerBlock), dim3(256), smem, st, true, (const float*)xa, (const float*)w_up, ids, (float*)hid, width, ff);
-  else
-    launch(moe_up_kernel<bf16>, dim3(tokens, top, (ff + kMoeRowsPerBlock - 1) / kMoeRowsPerBlock), dim3(256), smem, st, true, (const bf16*)xa, (const bf16*)w_up, ids, (bf16*)hid, width, ff);
-  return (int)cudaGetLastError();
+  return pk_moe_up_act(xa, w_up, ids, hid, tokens, top, width, ff, 0, f32, st);
 }
 
 extern "C" int pk_moe_down_combine(const void* hid, const void* w_down, const int* ids, const float* weights, const void* shared,

@@ -5,6 +5,7 @@
 //                            of 64-row tiles (expert, first slot).  Which slot a pair gets inside its expert's run may
 //                            vary from run to run; every row's result is independent of its slot, so outputs do not.
 //   2. moe_grouped_gemm<0>   hid[slot] = relu(W_up[e] x[token(slot)])^2          (rows gathered through the slot list)
+//      moe_grouped_gemm<2>   hid[slot] = silu(W_gate[e] x) * (W_up[e] x)            (gated experts, gate / up rows interleaved)
 //   3. moe_grouped_gemm<1>   part[slot] = weight(pair) * W_down[e] hid[slot]     (fp32)
 //   4. moe_combine_kernel    y[t] = sum_k part[slot(t, k)] (+ logistic(g_t) * shared[t]), summed in the order of k
 // GEMM tiles: 64 rows x 64 outputs x 64 deep, 4 warps of 32 x 32, mma.sync m16n8k16 bf16 with fp32 accumulation, operands
@@ -56,6 +57,7 @@ __global__ void moe_bucket_kernel(const int* __restrict__ ids, int pairs, int ex
 }
 
 // EPI 0: out bf16 [slots][N] = relu(acc)^2.   EPI 1: out fp32 [slots][N] = acc * weights[pair of the slot].
+// EPI 2: W rows interleaved (2f = gate f, 2f + 1 = up f): out bf16 [slots][N / 2] = silu(acc[2f]) * acc[2f + 1].
 // A row of slot s: A + (gather_div ? slot_pair[s] / gather_div : s) * K.
 template <int EPI>
 __global__ void __launch_bounds__(128) moe_grouped_gemm_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, void* __restrict__ out,
@@ -136,6 +138,8 @@ __global__ void __launch_bounds__(128) moe_grouped_gemm_kernel(const bf16* __res
           bf16* o = static_cast<bf16*>(out) + (size_t)s * N + n;
           if (n + 1 < N) *reinterpret_cast<uint32_t*>(o) = pack_bf16(v0 * v0, v1 * v1);
           else if (n < N) o[0] = f2bf(v0 * v0);
+        } else if (EPI == 2) {
+          if (n + 1 < N) static_cast<bf16*>(out)[(size_t)s * (N / 2) + n / 2] = f2bf(v0 / (1.f + expf(-v0)) * v1);
         } else {
           float* o = static_cast<float*>(out) + (size_t)s * N + n;
           if (n + 1 < N) *reinterpret_cast<float2*>(o) = make_float2(v0 * wgt, v1 * wgt);
@@ -172,10 +176,10 @@ extern "C" long pk_moe_grouped_workspace_bytes(int tokens, int top, int experts,
 }
 
 // y [tokens, width] fp32 = routed experts (+ gated shared expert); bf16 operands; width % 8 == 0 and ff % 8 == 0.
-extern "C" int pk_moe_grouped_relu2(const void* xa, const void* w_up, const void* w_down, const int* ids, const float* weights, const void* shared,
-                                    const float* shared_gate, float* y, void* workspace, int tokens, int top, int experts, int width, int ff,
-                                    pk_stream st) {
-  if (!xa || !w_up || !w_down || !ids || !weights || !y || !workspace || tokens <= 0 || top <= 0 || experts <= 0 || experts > 4096 || (shared && !shared_gate))
+extern "C" int pk_moe_grouped_act(const void* xa, const void* w_up, const void* w_down, const int* ids, const float* weights, const void* shared,
+                                  const float* shared_gate, float* y, void* workspace, int tokens, int top, int experts, int width, int ff, int act,
+                                  pk_stream st) {
+  if (!xa || !w_up || !w_down || !ids || !weights || !y || !workspace || tokens <= 0 || top <= 0 || experts <= 0 || experts > 4096 || (shared && !shared_gate) || act < 0 || act > 1)
     return -1;
   if (width % 8 || ff % 8 || (reinterpret_cast<uintptr_t>(xa) & 15) || (reinterpret_cast<uintptr_t>(w_up) & 15) ||
       (reinterpret_cast<uintptr_t>(w_down) & 15) || (reinterpret_cast<uintptr_t>(workspace) & 255))
@@ -192,11 +196,21 @@ extern "C" int pk_moe_grouped_relu2(const void* xa, const void* w_up, const void
   float* part = reinterpret_cast<float*>(ws + o);
   launch(moe_bucket_kernel, dim3(1), dim3(1024), (size_t)2 * experts * sizeof(int), st, true, ids, (int)pairs, experts, max_tiles, meta, slot_pair,
          pair_slot);
-  launch(moe_grouped_gemm_kernel<0>, dim3((ff + kGT - 1) / kGT, max_tiles), dim3(128), 0, st, true, (const bf16*)xa, (const bf16*)w_up, (void*)hid,
-         (const int*)meta, (const int*)slot_pair, weights, experts, max_tiles, ff, width, top);
+  if (act == 1)
+    launch(moe_grouped_gemm_kernel<2>, dim3((2 * ff + kGT - 1) / kGT, max_tiles), dim3(128), 0, st, true, (const bf16*)xa, (const bf16*)w_up, (void*)hid,
+           (const int*)meta, (const int*)slot_pair, weights, experts, max_tiles, 2 * ff, width, top);
+  else
+    launch(moe_grouped_gemm_kernel<0>, dim3((ff + kGT - 1) / kGT, max_tiles), dim3(128), 0, st, true, (const bf16*)xa, (const bf16*)w_up, (void*)hid,
+           (const int*)meta, (const int*)slot_pair, weights, experts, max_tiles, ff, width, top);
   launch(moe_grouped_gemm_kernel<1>, dim3((width + kGT - 1) / kGT, max_tiles), dim3(128), 0, st, true, (const bf16*)hid, (const bf16*)w_down,
          (void*)part, (const int*)meta, (const int*)slot_pair, weights, experts, max_tiles, width, ff, 0);
   launch(moe_combine_kernel, dim3(tokens), dim3(256), 0, st, true, (const float*)part, (const int*)pair_slot, (const bf16*)shared, shared_gate, y, width,
          top);
   return (int)cudaGetLastError();
+}
+
+extern "C" int pk_moe_grouped_relu2(const void* xa, const void* w_up, const void* w_down, const int* ids, const float* weights, const void* shared,
+                                    const float* shared_gate, float* y, void* workspace, int tokens, int top, int experts, int width, int ff,
+                                    pk_stream st) {
+  return pk_moe_grouped_act(xa, w_up, w_down, ids, weights, shared, shared_gate, y, workspace, tokens, top, experts, width, ff, 0, st);
 }

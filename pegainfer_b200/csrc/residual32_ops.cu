@@ -201,6 +201,60 @@ static inline int grid_1d(long n, int block) {
   return (int)(g < 1 ? 1 : (g > 148 * 16 ? 148 * 16 : g));
 }
 
+// ---- Dynamic Tanh, the norm of pre-norm blocks that computes no statistics: h = tanh(alpha * x) * w + b (alpha a scalar)
+// x[t] = float(embed[ids[t]]) * scale
+template <typename E>
+__global__ void embed_scaled_kernel(const E* __restrict__ embed, const int* __restrict__ tok, float* __restrict__ x, int width, float scale) {
+  pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
+  const int t = blockIdx.x;
+  const E* row = embed + (size_t)tok[t] * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) x[(size_t)t * width + i] = to_f(row[i]) * scale;
+}
+
+// x[t] += (ya[t] + yf[t]) (each optional: the sublayers of a parallel block), then h[t] = E(dyt(x[t])) and h32[t] = the same unrounded
+// (few-row fp32 projections read it).  w == null: only the sum (after the last layer).
+template <typename E>
+__global__ void add_dyt_kernel(const E* __restrict__ ya, const float* __restrict__ yf, const float* __restrict__ alpha, const E* __restrict__ w,
+                               const E* __restrict__ b, float* __restrict__ x, E* __restrict__ h, float* __restrict__ h32, long total, int width) {
+  pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
+  const float a = w ? alpha[0] : 0.f;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    float r = x[i];
+    if (ya || yf) {
+      const float y = (ya ? to_f(ya[i]) : 0.f) + (yf ? yf[i] : 0.f);
+      r += y;
+      x[i] = r;
+    }
+    if (w) {
+      const int c = (int)(i % width);
+      const float v = tanhf(a * r) * to_f(w[c]) + to_f(b[c]);
+      h[i] = from_f<E>(v);
+      if (h32) h32[i] = v;
+    }
+  }
+}
+
+// out[r] = E(dyt(x[rows[r]])): the model's last norm, only for the rows whose logits are wanted
+template <typename E>
+__global__ void dyt_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ alpha, const E* __restrict__ w,
+                                const E* __restrict__ b, E* __restrict__ out, int width) {
+  pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
+  const float* xr = x + (size_t)rows[blockIdx.x] * width;
+  const float a = alpha[0];
+  for (int i = threadIdx.x; i < width; i += blockDim.x) out[(size_t)blockIdx.x * width + i] = from_f<E>(tanhf(a * xr[i]) * to_f(w[i]) + to_f(b[i]));
+}
+
+// out = float(in) * scale (logits of a head with an output multiplier)
+template <typename A>
+__global__ void scale_to_f32_kernel(const A* __restrict__ in, float* __restrict__ out, long n, float scale) {
+  pdl_wait();
+  pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) out[i] = to_f(in[i]) * scale;
+}
+
 }  // namespace pk
 
 using namespace pk;
@@ -293,5 +347,40 @@ extern "C" int pk_gemm_strided(const void* A, const void* B, void* C, const floa
                     sbn, ldc, bsA, bsB, bsC, ld_scale, scale_kind),
              launch(gemm_strided_kernel<bf16>, g, b, 0, st, true, (const bf16*)A, (const bf16*)B, (bf16*)C, row_scale, rows, cols, K, lda, sbk, sbn,
                     ldc, bsA, bsB, bsC, ld_scale, scale_kind));
+  return (int)cudaGetLastError();
+}
+
+extern "C" int pk_res32_embed_scaled(const void* embed, const int* token_ids, float* x, int width, int tokens, float scale, int f32, pk_stream st) {
+  if (!embed || !token_ids || !x || width <= 0 || tokens <= 0) return -1;
+  PK_BY_TYPE(f32, launch(embed_scaled_kernel<float>, dim3(tokens), dim3(256), 0, st, true, (const float*)embed, token_ids, x, width, scale),
+             launch(embed_scaled_kernel<bf16>, dim3(tokens), dim3(256), 0, st, true, (const bf16*)embed, token_ids, x, width, scale));
+  return (int)cudaGetLastError();
+}
+
+extern "C" int pk_res32_add_dyt(const void* ya, const float* yf, const float* alpha, const void* w, const void* b, float* x, void* h, float* h32,
+                                int width, int tokens, int f32, pk_stream st) {
+  if (!x || width <= 0 || tokens <= 0 || (w && (!alpha || !b || !h)) || (!w && !ya && !yf)) return -1;
+  const long total = (long)width * tokens;
+  PK_BY_TYPE(f32,
+             launch(add_dyt_kernel<float>, dim3(grid_1d(total, 256)), dim3(256), 0, st, true, (const float*)ya, yf, alpha, (const float*)w, (const float*)b, x,
+                    (float*)h, h32, total, width),
+             launch(add_dyt_kernel<bf16>, dim3(grid_1d(total, 256)), dim3(256), 0, st, true, (const bf16*)ya, yf, alpha, (const bf16*)w, (const bf16*)b, x,
+                    (bf16*)h, h32, total, width));
+  return (int)cudaGetLastError();
+}
+
+extern "C" int pk_res32_dyt_rows(const float* x, const int* rows, const float* alpha, const void* w, const void* b, void* out, int width, int n_rows,
+                                 int f32, pk_stream st) {
+  if (!x || !rows || !alpha || !w || !b || !out || width <= 0 || n_rows <= 0) return -1;
+  PK_BY_TYPE(f32, launch(dyt_rows_kernel<float>, dim3(n_rows), dim3(256), 0, st, true, x, rows, alpha, (const float*)w, (const float*)b, (float*)out, width),
+             launch(dyt_rows_kernel<bf16>, dim3(n_rows), dim3(256), 0, st, true, x, rows, alpha, (const bf16*)w, (const bf16*)b, (bf16*)out, width));
+  return (int)cudaGetLastError();
+}
+
+extern "C" int pk_scale_to_f32(const void* in, int in_f32, float* out, long n, float scale, pk_stream st) {
+  if (!in || !out || n <= 0) return -1;
+  const dim3 g(grid_1d(n, 256)), b(256);
+  if (in_f32) launch(scale_to_f32_kernel<float>, g, b, 0, st, true, (const float*)in, out, n, scale);
+  else launch(scale_to_f32_kernel<bf16>, g, b, 0, st, true, (const bf16*)in, out, n, scale);
   return (int)cudaGetLastError();
 }

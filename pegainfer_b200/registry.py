@@ -18,6 +18,11 @@ def _load_vamadra(path, dtype, max_tokens, max_requests, **kw):
     return VamadraModel.from_pretrained(path, dtype=dtype, max_tokens=max_tokens, max_requests=max_requests, **kw)
 
 
+def _load_risolorn(path, dtype, max_tokens, max_requests, **kw):
+    from .risolorn import RisolornModel
+    return RisolornModel.from_pretrained(path, dtype=dtype, max_tokens=max_tokens, max_requests=max_requests, **kw)
+
+
 def _load_qwen3(path, dtype, max_tokens, max_requests, **kw):
     from .config import PAGE_SIZE
     from .model import ModelRuntimeConfig, Qwen3Model
@@ -30,11 +35,12 @@ def _load_qwen3(path, dtype, max_tokens, max_requests, **kw):
 # design name (as a checkpoint spells it) -> loader
 ARCHITECTURES = {
     "Vamadra": _load_vamadra,
+    "Risolorn": _load_risolorn,
     "Qwen3ForCausalLM": _load_qwen3,
     "qwen3": _load_qwen3,
 }
 # designs whose kernels run with every product in fp32 as well
-FLOAT32_CAPABLE = {"Vamadra"}
+FLOAT32_CAPABLE = {"Vamadra", "Risolorn"}
 
 
 def architecture_of(model_path: str) -> str:
