@@ -126,6 +126,20 @@ RES32_SIGNATURES = {
     "pk_moe_down_combine": (i32, [vp] * 7 + [i32, i32, i32, i32, i32, vp]),
     "pk_moe_grouped_workspace_bytes": (i64l, [i32, i32, i32, i32, i32]),
     "pk_moe_grouped_relu2": (i32, [vp] * 9 + [i32, i32, i32, i32, i32, vp]),
+    # parallel pre-norm blocks, grouped-query attention with sink / chunks, recurrent mixers, router / expert options
+    "pk_res32_embed_scaled": (i32, [vp, vp, vp, i32, i32, f32, i32, vp]),
+    "pk_res32_add_dyt": (i32, [vp] * 8 + [i32, i32, i32, vp]),
+    "pk_res32_dyt_rows": (i32, [vp] * 6 + [i32, i32, i32, vp]),
+    "pk_scale_to_f32": (i32, [vp, i32, vp, i64l, f32, vp]),
+    "pk_gqa_rope_append": (i32, [vp, i32, vp, vp, vp, vp, vp, vp, vp, i64l] + [i32] * 7 + [vp, f32, i32, i32, vp]),
+    "pk_gqa_attention": (i32, [vp] * 8 + [i64l] + [i32] * 6 + [f32, i32, i32, vp]),
+    "pk_causal_conv_silu": (i32, [vp, i32, vp, vp, i64l, vp, vp, vp, vp, vp] + [i32] * 6 + [vp]),
+    "pk_gated_delta_seq": (i32, [vp, i32, i32, i32, i32, vp, i32, i32, i32, vp, vp, vp, i64l, vp, vp, vp, vp] + [i32] * 6 + [vp]),
+    "pk_mlstm_seq": (i32, [vp, i32, i32, i32, i32, vp, i32, i32, i32, vp, vp, f32, vp, i64l, vp, vp, vp, vp, vp] + [i32] * 5 + [vp]),
+    "pk_head_norm_gate": (i32, [vp, vp, vp, i32, vp, i32, i32, vp, i32, i32, i32, f32, i32, i32, vp]),
+    "pk_router_topk_ex": (i32, [vp, i32, vp, vp, vp] + [i32] * 5 + [f32, i32, i32, i32, vp]),
+    "pk_moe_up_act": (i32, [vp, vp, vp, vp] + [i32] * 6 + [vp]),
+    "pk_moe_grouped_act": (i32, [vp] * 9 + [i32] * 6 + [vp]),
 }
 
 

@@ -1,0 +1,597 @@
+"""Risolorn on the GPU against the plain fp32 oracle (oracle/risolorn_oracle.py): mechanisms alone through the C ABI or as
+one-layer models, then the model through its own step / engine / generate entry points -- whole prompts, token-by-token
+decoding, portions down to two tokens, unequal batches, reused pages and state slots, keys far back, at page borders and on
+both sides of chunk edges, the first tokens, long decoding, greedy generation.
+
+Configurations and weights are made here (small, random, seeded).  float32 runs are held to 2e-4 of the logits' spread,
+bfloat16 runs to rounding noise.  Where random weights would blur a fault (one far key among hundreds, the sink, a chunk's
+edge) the inputs are built so that a single score dominates.
+"""
+import math
+
+import pytest
+import torch
+
+from oracle import risolorn_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+F32, BF16 = torch.float32, torch.bfloat16
+YARN = {"factor": 4.0, "original": 64, "fast": 16.0, "slow": 2.0}
+
+
+# ------------------------------------------------------------------ configurations (none is a real checkpoint's)
+def attn(heads, kv_heads, dim, vdim, chunk, rot_dims=None, scaling=True, base=10000.0, scale=None):
+    rot = {"dims": dim if rot_dims is None else rot_dims, "base": base}
+    if scaling:
+        rot["scaling"] = dict(YARN)
+    return {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "mask": {"size": chunk}, "rot": rot,
+                                           "scale": scale if scale is not None else 1.0 / math.sqrt(dim)}}
+
+
+def delta(heads, kv_heads, dim, vdim, conv):
+    return {"type": "delta", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv}}
+
+
+def mlstm(heads, dim, vdim, cap):
+    return {"type": "mlstm", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "gate_cap": cap}}
+
+
+def moe(experts, top, count, keep, ff):
+    return {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top, "groups": {"count": count, "keep": keep}}}
+
+
+def model_cfg(layers, vocab=211, width=88, eps=1e-5, embed=2.0, logit=0.7):
+    return {"architecture": "Risolorn", "vocab": vocab, "width": width, "norm": {"eps": eps}, "embedding": {"scale": embed}, "logit_scale": logit,
+            "layers": [dict(l, mlp=m) for l, m in layers]}
+
+
+def cfg_general():
+    """All sizes differ from each other; every mixer; a layer without feed-forward; the bf16 attention of layer 1 takes the tensor-core
+    kernel for its prompt portions, layer 3 the generic one."""
+    return model_cfg([(delta(4, 2, 24, 40, 4), moe(8, 2, 4, 2, 56)),
+                      (attn(6, 2, 32, 32, 48, rot_dims=16), moe(8, 3, 2, 1, 40)),
+                      (mlstm(3, 16, 24, 10.0), None),
+                      (attn(4, 4, 24, 40, 37, scaling=False, base=500.0), moe(6, 3, 1, 1, 48))])
+
+
+def cfg_edges():
+    """Values that often coincide or equal one are made to differ: one head, kv_heads == heads, top 1, keep == count, one expert per
+    group, a one-tap and a two-tap convolution, a chunk of five tokens, widths that are no multiple of 8."""
+    return model_cfg([(attn(1, 1, 12, 20, 5, rot_dims=8), moe(4, 1, 4, 4, 28)),
+                      (delta(2, 2, 12, 12, 1), None),
+                      (mlstm(1, 40, 8, 3.0), moe(6, 2, 3, 2, 20)),
+                      (delta(3, 1, 8, 36, 2), moe(4, 4, 2, 2, 12))], vocab=97, width=52, eps=1e-6, embed=0.5, logit=1.5)
+
+
+def cfg_wide_heads():
+    """head sizes the 128-wide register tiles take; chunk = a multiple of the page size"""
+    return model_cfg([(attn(4, 1, 64, 64, 64), moe(4, 2, 1, 1, 64)), (delta(2, 1, 128, 64, 3), None), (mlstm(2, 96, 72, 15.0), None)],
+                     vocab=128, width=64)
+
+
+def one_layer(l, mlp=None):
+    return model_cfg([(l, mlp)], vocab=64, width=48)
+
+
+def make_weights(cfg, seed, sharp=1.0):
+    """bf16 checkpoint; `sharp` scales the query projections of attention layers so that the softmax is peaked on single keys."""
+    from pegainfer_b200.risolorn import RisolornConfig, weight_shapes
+    g = torch.Generator().manual_seed(seed)
+    kinds = [l["type"] for l in cfg["layers"]]
+    w = {}
+    for name, shape in weight_shapes(RisolornConfig.from_dict(cfg)).items():
+        leaf = name.rsplit(".", 1)[-1]
+        rn = lambda s=1.0: s * torch.randn(shape, generator=g)  # noqa: E731
+        if leaf == "alpha":
+            t = torch.tensor(0.6) + 0.2 * rn()
+        elif name.endswith(("norm1", "final.norm", "mix.norm")):
+            t = 1.0 + 0.2 * rn()
+        elif leaf == "conv":
+            t = rn(0.6)
+        elif leaf == "correction":
+            t = rn(0.5)
+        elif leaf == "A_log":
+            t = rn(0.7) - 1.0
+        elif leaf == "sink":
+            t = rn(1.5)
+        elif len(shape) <= 1:
+            t = rn(0.4)
+        elif name == "embed":
+            t = rn()
+        else:
+            t = rn() / math.sqrt(shape[1])
+            if name.endswith("mix.q") and kinds[int(name[1:name.index(".")])] == "attention":
+                t = t * sharp
+            if leaf == "router" or name.endswith(("mix.i", "mix.f", "mix.a", "mix.b")):
+                t = t * 3.0
+        w[name] = t.to(BF16)
+    return w
+
+
+def build(cfg, w, dtype, max_tokens=1024, max_requests=4):
+    from pegainfer_b200.risolorn import RisolornConfig, RisolornModel
+    return RisolornModel(RisolornConfig.from_dict(cfg), w, dtype=dtype, max_tokens=max_tokens, max_requests=max_requests)
+
+
+def row_errors(got, want):
+    d = got - want
+    d = d - d.mean(-1, keepdim=True)
+    return d.pow(2).mean(-1).sqrt() / (want - want.mean(-1, keepdim=True)).pow(2).mean().sqrt()
+
+
+def close(got, want, dtype):
+    """float32: every row within 2e-4 of the logits' spread.  bfloat16: rounding noise only -- half of the rows within 4 %, 85 in
+    100 within 10 % (a routing decision that rounding flips moves single rows; a wrong key, mask, state or page shows in the
+    float32 run of the same test)."""
+    e = row_errors(got, want)
+    if dtype == F32:
+        return e.max().item() < 2e-4
+    return e.median().item() < 0.04 and e.quantile(0.85).item() < 0.10
+
+
+SHARP = {F32: 5.0, BF16: 2.0}
+CONFIGS = {"general": cfg_general, "edges": cfg_edges, "wide": cfg_wide_heads}
+
+
+def tokens_for(cfg, n, seed):
+    return torch.randint(0, cfg["vocab"], (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+def oracle_logits(cfg, w, toks, trail=None):
+    return O.forward(cfg, w, toks, trail)
+
+
+# ------------------------------------------------------------------ kernels alone
+@pytest.fixture(scope="module")
+def lib():
+    from pegainfer_b200 import ffi
+    ffi.lib().cublas_init()
+    return ffi.lib()
+
+
+def dev(t, dtype):
+    return t.to(dtype).cuda().contiguous()
+
+
+def i32(xs):
+    return torch.tensor(xs, dtype=torch.int32, device="cuda")
+
+
+class Hold:
+    """ptr(t) returns t's device address and keeps t alive until the launches that read it are done."""
+
+    def __init__(self):
+        self.kept = []
+
+    def __call__(self, t):
+        self.kept.append(t)
+        return t.data_ptr()
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_dynamic_tanh_with_residual_sum(lib, dtype):
+    P = Hold()
+    T, W = 7, 52
+    g = torch.Generator().manual_seed(1)
+    x, ya, yf = torch.randn(T, W, generator=g), torch.randn(T, W, generator=g).to(dtype).to(F32), torch.randn(T, W, generator=g)
+    w = {"n": (1 + 0.3 * torch.randn(W, generator=g)).to(dtype), "n.b": (0.3 * torch.randn(W, generator=g)).to(dtype), "n.alpha": torch.tensor(0.37)}
+    xd, h, h32 = x.cuda(), torch.zeros(T, W, dtype=dtype, device="cuda"), torch.zeros(T, W, device="cuda")
+    rc = lib.pk_res32_add_dyt(P(dev(ya, dtype)), P(yf.cuda()), P(w["n.alpha"].reshape(1).cuda()), P(w["n"].cuda()), P(w["n.b"].cuda()), xd.data_ptr(),
+                              h.data_ptr(), h32.data_ptr(), W, T, int(dtype == F32), None)
+    torch.cuda.synchronize()
+    assert rc == 0
+    xs = x + (ya + yf)
+    want = O.dyt(xs, w, "n")
+    assert torch.allclose(xd.cpu(), xs, atol=1e-6)
+    assert torch.allclose(h32.cpu(), want, atol=2e-6)
+    assert torch.allclose(h.float().cpu(), want, atol=1e-6 if dtype == F32 else 2e-2)
+
+
+def paged(req_lens, page_size, shuffle_seed=0):
+    """A page table with pages handed out in a scrambled order: (pages flat, page_off per request, number of pages)."""
+    need = [(n + page_size - 1) // page_size for n in req_lens]
+    order = torch.randperm(sum(need) + 3, generator=torch.Generator().manual_seed(shuffle_seed)).tolist()
+    pages, off, k = [], [], 0
+    for n in need:
+        off.append(len(pages))
+        pages += order[k:k + n]
+        k += n
+    return pages, off, sum(need) + 3
+
+
+def run_attention(lib, dtype, mx, qkv, bias, sink, pos, req, starts, lens, ps=16):
+    """Rotation + cache append + attention for a step whose request r brings positions starts[r] .. lens[r] - 1 (earlier positions were
+    appended by a first call from `qkv` rows of the same tensor).  qkv: per request [len, nq + nk + nv].  Returns [T, H * vdim]."""
+    P = Hold()
+    H, G, D, Dv = mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"]
+    n_all = H * D + G * D + G * Dv
+    pages, off, n_pages = paged(lens, ps, shuffle_seed=5)
+    stride = ps * G * (D + Dv) + 24
+    cache = torch.zeros(n_pages, stride, dtype=dtype, device="cuda")
+    f, mag = O.rotary_frequencies(mx["rot"])
+    f = f.to(F32).cuda()
+    f32 = int(dtype == F32)
+
+    def step(rows_of):  # rows_of[r] = (first position, one past the last)
+        x = torch.cat([qkv[r][a:b] for r, (a, b) in enumerate(rows_of)])
+        p = [q for a, b in rows_of for q in range(a, b)]
+        rq = [r for r, (a, b) in enumerate(rows_of) for _ in range(a, b)]
+        T = len(p)
+        if T == 0:
+            return None
+        qo, out = torch.zeros(T, H * D, dtype=dtype, device="cuda"), torch.zeros(T, H * Dv, dtype=dtype, device="cuda")
+        a = (P(i32(p)), P(i32(rq)), P(i32(off)), P(i32(pages)))
+        assert lib.pk_gqa_rope_append(P(dev(x, dtype)), n_all, P(dev(bias, dtype)), *a, qo.data_ptr(), cache.data_ptr(), stride, ps, H, G, D, Dv,
+                                      mx["rot"]["dims"], 1, f.data_ptr(), float(mag), T, f32, None) == 0
+        assert lib.pk_gqa_attention(qo.data_ptr(), cache.data_ptr(), P(dev(sink, dtype)), *a, out.data_ptr(), stride, ps, T, H, G, D, Dv,
+                                    float(mx["scale"]), mx["mask"]["size"], f32, None) == 0
+        torch.cuda.synchronize()
+        return out.float().cpu()
+
+    step([(0, s) for s in starts])
+    return step([(s, n) for s, n in zip(starts, lens)])
+
+
+def oracle_attention(mx, qkv, bias, sink, lo, hi):
+    """The oracle's attention mixer with identity projections: its input `h` IS the stacked projection output."""
+    H, G, D, Dv = mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"]
+    nq, nk, nv = H * D, G * D, G * Dv
+    eye = torch.eye(nq + nk + nv)
+    w = {"q": eye[:nq], "k": eye[nq:nq + nk], "v": eye[nq + nk:], "q.b": bias[:nq], "k.b": bias[nq:nq + nk], "v.b": bias[nq + nk:], "sink": sink,
+         "o": torch.eye(H * Dv)}
+    return O.attention_mixer(qkv[:hi], w, "", mx, torch.arange(hi))[lo:]
+
+
+# (heads, kv heads, dim, vdim, chunk, rotated entries): bf16 prompts with dim == vdim in {32, 64, 128} run on the tensor cores
+ATTN_SHAPES = [(3, 1, 20, 12, 50, 8), (6, 2, 32, 32, 48, 32), (4, 4, 64, 64, 100, 16), (2, 1, 128, 128, 64, 128), (5, 5, 40, 72, 33, 40)]
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("H,G,D,Dv,chunk,dims", ATTN_SHAPES)
+def test_attention_ragged_batch(lib, dtype, H, G, D, Dv, chunk, dims):
+    """three requests in one launch: a 70-token portion that starts at position 90 and crosses chunk edges, one decoded token at
+    position 199, and the first 5 tokens of a sequence"""
+    mx = attn(H, G, D, Dv, chunk, rot_dims=dims)["mixer"]
+    g = torch.Generator().manual_seed(3)
+    lens, starts = [160, 200, 5], [90, 199, 0]
+    n_all = H * D + G * D + G * Dv
+    qkv = [torch.randn(n, n_all, generator=g).to(dtype).to(F32) for n in lens]
+    for x in qkv:
+        x[:, :H * D] *= 2.0
+    bias, sink = (0.3 * torch.randn(n_all, generator=g)).to(dtype).to(F32), (1.5 * torch.randn(H, generator=g)).to(dtype).to(F32)
+    got = run_attention(lib, dtype, mx, qkv, bias, sink, None, None, starts, lens)
+    want = torch.cat([oracle_attention(mx, qkv[r], bias, sink, starts[r], lens[r]) for r in range(3)])
+    tol = 3e-5 if dtype == F32 else 4e-2
+    assert torch.allclose(got, want, atol=tol, rtol=tol)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("prompt", [False, True])
+def test_attention_single_keys_stand_out(lib, dtype, prompt):
+    """One key is aimed at with a steep score, so the output must be that key's value: far back in the chunk, on both sides of page
+    borders, at the chunk's first position and at the query's own.  A key just before the chunk's first position, or one past the
+    query, is hidden: the output must then NOT be its value (and equal the oracle's, as in every case).  `prompt`: the queries sit
+    in a 40-token portion (bf16: tensor-core kernel), else they are decoded tokens."""
+    H, D, chunk = 2, 32, 512
+    mx = attn(H, 1, D, D, chunk, rot_dims=0, scaling=False, scale=1.0)["mixer"]
+    n = 700
+    g = torch.Generator().manual_seed(4)
+    val = torch.randn(n, D, generator=g).to(dtype).to(F32)
+    key = torch.nn.functional.normalize(torch.randn(n, D, generator=g), dim=-1)
+    sink = torch.full((H,), 15.0)
+    # (query position, key aimed at, visible?)
+    cases = [(690, 512, True), (690, 511, False), (690, 530, True), (690, 690, True), (690, 691, False), (690, 671, True), (690, 672, True),
+             (500, 3, True), (500, 0, True), (500, 15, True), (500, 16, True), (511, 0, True), (512, 511, False), (512, 512, True)]
+    for qp, kp, visible in cases:
+        qkv = torch.zeros(n, H * D + 2 * D)
+        qkv[:, H * D:H * D + D], qkv[:, H * D + D:] = key, val
+        qkv[qp, :D] = 30.0 * key[kp]  # head 0 aims at position kp; head 1 asks nothing (uniform scores)
+        qkv = qkv.to(dtype).to(F32)
+        hi = max(qp, kp) + 1
+        start = qp - 39 if prompt else qp
+        bias = torch.zeros(H * D + 2 * D)
+        got = run_attention(lib, dtype, mx, [qkv], bias, sink, None, None, [start], [hi])[qp - start]
+        want = oracle_attention(mx, qkv, bias, sink, qp, hi)[0]
+        assert torch.allclose(got, want, atol=1e-4 if dtype == F32 else 6e-2), (qp, kp)
+        if visible:
+            assert torch.allclose(got[:D], val[kp], atol=2e-2 if dtype == F32 else 8e-2), (qp, kp)
+        else:
+            assert (got[:D] - val[kp]).norm() > 0.5 * val[kp].norm(), (qp, kp)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("taps", [1, 2, 4])
+def test_short_convolution_carries_its_tail_through_portions(lib, dtype, taps):
+    """two requests, fed in portions of 1, 2, 3 and 7 tokens in turn (shorter and longer than the tail), slots swapped"""
+    P = Hold()
+    C, ld = 20, 27
+    g = torch.Generator().manual_seed(5)
+    xs = [torch.randn(30, C, generator=g).to(dtype).to(F32), torch.randn(22, C, generator=g).to(dtype).to(F32)]
+    cw = (0.7 * torch.randn(C, taps, generator=g)).to(dtype).to(F32)
+    want = [O.causal_conv_silu(x, cw) for x in xs]
+    slot_stride = 5 + max(taps - 1, 0) * C
+    state = torch.zeros(3, slot_stride, device="cuda")
+    slots, at, got = [2, 0], [0, 0], [[], []]
+    sizes = [1, 2, 3, 7]
+    k = 0
+    while at[0] < 30 or at[1] < 22:
+        take = [min(sizes[(k + r) % 4], len(xs[r]) - at[r]) for r in range(2)]
+        ents = [r for r in range(2) if take[r] > 0]
+        x = torch.zeros(sum(take), ld)
+        x[:, 3:3 + C] = torch.cat([xs[r][at[r]:at[r] + take[r]] for r in ents])
+        req = [e for e, r in enumerate(ents) for _ in range(take[r])]
+        row0 = [sum(take[q] for q in ents[:e]) for e in range(len(ents))]
+        out = torch.zeros(sum(take), C, dtype=dtype, device="cuda")
+        xd = dev(x, dtype)
+        rc = lib.pk_causal_conv_silu(xd.data_ptr() + 3 * xd.element_size(), ld, P(dev(cw, dtype)), state.data_ptr() + 5 * 4, slot_stride, P(i32(req)),
+                                     P(i32([slots[r] for r in ents])), P(i32(row0)), P(i32([take[r] for r in ents])), out.data_ptr(), C, C, taps,
+                                     sum(take), len(ents), int(dtype == F32), None)
+        torch.cuda.synchronize()
+        assert rc == 0
+        for e, r in enumerate(ents):
+            got[r].append(out[row0[e]:row0[e] + take[r]].float().cpu())
+            at[r] += take[r]
+        k += 1
+    for r in range(2):
+        assert torch.allclose(torch.cat(got[r]), want[r], atol=1e-5 if dtype == F32 else 3e-2)
+    assert (state[1] == 0).all() and (state[:, :5] == 0).all()  # the unused slot and the words before the block stay untouched
+
+
+@pytest.mark.parametrize("E,top,count,keep", [(8, 2, 4, 2), (12, 4, 3, 2), (6, 3, 1, 1), (4, 1, 4, 4), (6, 2, 6, 3), (64, 6, 8, 3)])
+def test_router_choice_and_weights(lib, E, top, count, keep):
+    """logistic scores, correction for the choice only, groups by their two best corrected scores; negative corrected scores must
+    still beat a closed group"""
+    P = Hold()
+    T, ld = 50, E + 3
+    g = torch.Generator().manual_seed(6)
+    z = 2.0 * torch.randn(T, ld, generator=g)
+    corr = 0.8 * torch.randn(E, generator=g) - 1.5  # most corrected scores are negative
+    ids, wts = torch.zeros(T, top, dtype=torch.int32, device="cuda"), torch.zeros(T, top, device="cuda")
+    rc = lib.pk_router_topk_ex(P(z.cuda()), ld, P(corr.cuda()), ids.data_ptr(), wts.data_ptr(), T, E, top, count, keep, 1.0, 1, 2, 0, None)
+    torch.cuda.synchronize()
+    assert rc == 0
+    eye = torch.eye(E)
+    want_ids, want_w = O.route(z[:, :E], {"router": eye, "correction": corr}, "", {"experts": E, "top": top, "groups": {"count": count, "keep": keep}})
+    assert (ids.cpu().long().sort(-1).values == want_ids.sort(-1).values).all()
+    order = ids.cpu().long().argsort(-1)
+    assert torch.allclose(wts.cpu().gather(1, order), want_w.gather(1, want_ids.argsort(-1)), atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("T", [3, 70])
+def test_gated_experts(lib, dtype, T):
+    """per-token form (few tokens, both element types) and the bucketed tensor-core form (bf16, many tokens) of the gated experts"""
+    P = Hold()
+    E, top, W, ff = 5, 2, 48, 40
+    g = torch.Generator().manual_seed(7)
+    h = torch.randn(T, W, generator=g).to(dtype).to(F32)
+    w = {"router": torch.randn(E, W, generator=g), "correction": torch.zeros(E)}
+    for e in range(E):
+        w[f"e{e}.gate"], w[f"e{e}.up"] = (torch.randn(ff, W, generator=g) / 7).to(dtype), (torch.randn(ff, W, generator=g) / 7).to(dtype)
+        w[f"e{e}.down"] = (torch.randn(W, ff, generator=g) / 6).to(dtype)
+    mlp = moe(E, top, 1, 1, ff)
+    ids, wt = O.route(h, w, "", mlp["router"])
+    want = O.moe(h, w, "", mlp)
+    up = torch.stack([torch.stack([w[f"e{e}.gate"], w[f"e{e}.up"]], 1).reshape(2 * ff, W) for e in range(E)])  # rows interleaved
+    down = torch.stack([w[f"e{e}.down"] for e in range(E)])
+    idd, wd = P(ids.to(torch.int32).cuda()), P(wt.cuda())
+    y = torch.zeros(T, W, device="cuda")
+    f32 = int(dtype == F32)
+    if dtype == BF16 and T >= 32:
+        ws = torch.zeros(lib.pk_moe_grouped_workspace_bytes(T, top, E, W, ff) + 256, dtype=torch.uint8, device="cuda")
+        base = (ws.data_ptr() + 255) // 256 * 256
+        assert lib.pk_moe_grouped_act(P(dev(h, dtype)), P(dev(up, dtype)), P(dev(down, dtype)), idd, wd, None, None, y.data_ptr(), base, T, top, E, W, ff, 1,
+                                      None) == 0
+    else:
+        hid = torch.zeros(T, top, ff, dtype=dtype, device="cuda")
+        assert lib.pk_moe_up_act(P(dev(h, dtype)), P(dev(up, dtype)), idd, hid.data_ptr(), T, top, W, ff, 1, f32, None) == 0
+        assert lib.pk_moe_down_combine(hid.data_ptr(), P(dev(down, dtype)), idd, wd, None, None, y.data_ptr(), T, top, W, ff, f32, None) == 0
+    torch.cuda.synchronize()
+    assert torch.allclose(y.cpu(), want, atol=1e-5 if dtype == F32 else 3e-2, rtol=1e-5 if dtype == F32 else 3e-2)
+
+
+# ------------------------------------------------------------------ one mechanism per model
+MIXERS = {"attention": attn(3, 1, 16, 24, 21, rot_dims=12), "delta": delta(4, 2, 16, 24, 3), "delta_wide": delta(2, 1, 72, 136, 4),
+          "mlstm": mlstm(3, 24, 16, 6.0), "mlstm_wide": mlstm(2, 136, 100, 12.0)}
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("name", sorted(MIXERS))
+def test_one_mixer_alone(name, dtype):
+    """a one-layer model without feed-forward: the residual after the layer is embedding + mixer(norm(embedding))"""
+    cfg = one_layer(MIXERS[name])
+    w = make_weights(cfg, 11)
+    toks = tokens_for(cfg, 75, 1)
+    m = build(cfg, w, dtype)
+    m.keep_trail(True)
+    rid = m.alloc_request()
+    m.step([(rid, toks)], [[len(toks) - 1]])
+    got = m.trail(len(toks))[0]
+    trail = []
+    oracle_logits(cfg, w, toks, trail)
+    x0 = O.f32(w["embed"])[torch.tensor(toks)] * cfg["embedding"]["scale"]
+    err = (got - trail[0]).abs().max() / (trail[0] - x0).abs().max()
+    assert err < (2e-5 if dtype == F32 else 4e-2)
+    m.close()
+
+
+# ------------------------------------------------------------------ the model through its own entry points
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+def test_whole_prompt_with_residual_after_every_layer(name, dtype):
+    cfg = CONFIGS[name]()
+    w = make_weights(cfg, 21, SHARP[dtype])
+    toks = tokens_for(cfg, 150, 2)
+    m = build(cfg, w, dtype)
+    m.keep_trail(True)
+    rid = m.alloc_request()
+    got = m.step([(rid, toks)], [list(range(len(toks)))])
+    trail = []
+    want = oracle_logits(cfg, w, toks, trail)
+    tr = m.trail(len(toks))
+    for i, x in enumerate(trail):
+        e = (tr[i] - x).abs().max() / x.abs().max()
+        assert e < (1e-4 if dtype == F32 else 0.2), (i, e)
+    assert close(got, want, dtype)
+    m.close()
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+def test_prefill_against_token_by_token_decoding(name, dtype):
+    """the first tokens as one prompt, the rest one by one through the cache and the state slots (chunk edges of every attention
+    layer are crossed while decoding); then the same sequence decoded from its very first token"""
+    cfg = CONFIGS[name]()
+    w = make_weights(cfg, 22, SHARP[dtype])
+    toks = tokens_for(cfg, 130, 3)
+    want = oracle_logits(cfg, w, toks)
+    m = build(cfg, w, dtype)
+    for first in (60, 1):
+        rid = m.alloc_request()
+        rows = [m.step([(rid, toks[:first])], [list(range(first))])]
+        for t in range(first, len(toks)):
+            rows.append(m.step([(rid, [toks[t]])]))
+        assert close(torch.cat(rows), want, dtype), first
+        m.drop_request(rid)
+    m.close()
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("sizes", [(2,), (3, 2, 16, 1, 37, 5), (64, 2, 2), (33, 1)])
+def test_prompt_in_portions(dtype, sizes):
+    """portions cut anywhere (inside pages, chunks and the convolutions' tails), down to two tokens"""
+    cfg = cfg_general()
+    w = make_weights(cfg, 23, SHARP[dtype])
+    toks = tokens_for(cfg, 140, 4)
+    want = oracle_logits(cfg, w, toks)
+    m = build(cfg, w, dtype)
+    rid = m.alloc_request()
+    rows, at, k = [], 0, 0
+    while at < len(toks):
+        n = min(sizes[k % len(sizes)], len(toks) - at)
+        rows.append(m.step([(rid, toks[at:at + n])], [list(range(n))]))
+        at, k = at + n, k + 1
+    assert close(torch.cat(rows), want, dtype)
+    m.close()
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_unequal_batches_reuse_pages_and_slots(dtype):
+    """Seven unequal requests through three request slots and a pool of 18 pages: portions of some beside single tokens of others in
+    every step; finished requests hand their pages and state slot to the next one.  Every request must come out as when it runs alone."""
+    from pegainfer_b200.engine import Engine
+    cfg = cfg_general()
+    w = make_weights(cfg, 24, SHARP[dtype])
+    lens = [70, 9, 40, 101, 1, 33, 64]
+    prompts = [tokens_for(cfg, n, 30 + i) for i, n in enumerate(lens)]
+    want = [oracle_logits(cfg, w, p) for p in prompts]
+    m = build(cfg, w, dtype, max_tokens=18 * 16, max_requests=3)
+    eng = Engine(m)
+    got = [[] for _ in prompts]
+    at = [0] * len(prompts)
+    waiting, live, step, seen_pages = list(range(len(prompts))), [], 0, set()
+    portion = [5, 1, 17, 2, 1, 30, 3]
+    pages_of = lambda i: (lens[i] + 15) // 16  # noqa: E731
+    while waiting or live:
+        while waiting and len(live) < 3 and sum(pages_of(i) for i in live) + pages_of(waiting[0]) <= 18:
+            live.append(waiting.pop(0))
+        entries, end = [], []
+        for i in live:
+            n = min(portion[(step + i) % len(portion)], lens[i] - at[i])
+            entries.append((f"q{i}", prompts[i][at[i]:at[i] + n], list(range(n))))
+        out = eng.step(entries, [])
+        r = 0
+        for (name, t, _), i in zip(entries, list(live)):
+            got[i].append(out[r:r + len(t)])
+            r += len(t)
+            at[i] += len(t)
+            seen_pages.update(m.request_pages(eng.slots[name]))
+            if at[i] == lens[i]:
+                eng.release(name)
+                live.remove(i)
+        step += 1
+    assert sum((n + 15) // 16 for n in lens) > 18 >= len(seen_pages)  # pages were handed out again
+    for i in range(len(prompts)):
+        assert close(torch.cat(got[i]), want[i], dtype), i
+    m.close()
+
+
+def test_rejected_step_leaves_lengths_pages_and_state_untouched():
+    cfg = cfg_general()
+    w = make_weights(cfg, 25)
+    toks = tokens_for(cfg, 60, 5)
+    m = build(cfg, w, F32, max_tokens=64, max_requests=2)
+    a, b = m.alloc_request(), m.alloc_request()
+    m.step([(a, toks[:20])])
+    free = m.available_pages()
+    with pytest.raises(RuntimeError):
+        m.step([(a, toks[20:25]), (b, toks[:60])])  # b does not fit: nothing of the step may stay
+    assert m.seq_len(a) == 20 and m.seq_len(b) == 0 and m.available_pages() == free
+    got = m.step([(a, toks[20:40])], [list(range(20))])
+    assert close(got, oracle_logits(cfg, w, toks[:40])[20:], F32)
+    m.close()
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_long_decoding_and_captured_steps(dtype):
+    """a 300-token prompt and 260 decoded tokens (captured launch sequences from the second step of a kind on, across a graph bucket
+    border at 512) against the same steps run eagerly and against the oracle"""
+    cfg = model_cfg([(attn(4, 2, 32, 32, 128, rot_dims=16), moe(8, 2, 4, 2, 32)), (delta(2, 2, 32, 32, 4), None), (mlstm(2, 32, 32, 8.0), moe(4, 2, 1, 1, 32))],
+                    vocab=96, width=64)
+    w = make_weights(cfg, 26, SHARP[dtype])
+    toks = tokens_for(cfg, 560, 6)
+    outs = []
+    for graph in (True, False):
+        m = build(cfg, w, dtype, max_tokens=1024)
+        m.use_graph(graph)
+        rid = m.alloc_request()
+        rows = [m.step([(rid, toks[:300])])]
+        for t in range(300, 560):
+            rows.append(m.step([(rid, [toks[t]])]))
+        assert (m.graph_count() > 0) == graph
+        outs.append(torch.cat(rows))
+        m.close()
+    assert torch.allclose(outs[0], outs[1], atol=1e-5 if dtype == F32 else 2e-2)
+    want = oracle_logits(cfg, w, toks)[299:]
+    assert close(outs[0], want, dtype)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_greedy_generation_through_the_scheduler(dtype):
+    """the framework's own entry points: generate() of the model and the continuous-batching scheduler; teacher-forced check of
+    every generated token against the oracle's logits for the sequence the framework produced"""
+    from pegainfer_b200.engine import Engine
+    cfg = cfg_general()
+    w = make_weights(cfg, 27)
+    prompts = [tokens_for(cfg, n, 40 + n) for n in (5, 37, 1, 64, 18)]
+    m = build(cfg, w, dtype, max_tokens=512, max_requests=3)
+    outs = Engine(m).generate(prompts, 12, max_live=3, token_budget=48)
+    alone, _, _ = m.generate(prompts[1], 12)
+    for p, o in zip(prompts, outs):
+        assert len(o) == 12
+        lg = oracle_logits(cfg, w, p + o[:-1])[len(p) - 1:]
+        top2 = lg.topk(2, -1).values
+        gap_ok = (top2[:, 0] - top2[:, 1]) < (1e-3 if dtype == F32 else 0.15) * lg.std()
+        assert ((lg.argmax(-1) == torch.tensor(o)) | gap_ok).all()
+    if dtype == F32:
+        assert alone == outs[1]
+    m.close()
+
+
+def test_checkpoint_folder_through_the_registry(tmp_path):
+    import json
+
+    from safetensors.torch import save_file
+
+    from pegainfer_b200.registry import architecture_of, load_model
+    cfg = cfg_edges()
+    w = make_weights(cfg, 28)
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    save_file({k: v.contiguous() for k, v in w.items()}, str(tmp_path / "model.safetensors"))
+    assert architecture_of(str(tmp_path)) == "Risolorn"
+    m = load_model(str(tmp_path), "float32", max_tokens=256)
+    toks = tokens_for(cfg, 40, 7)
+    rid = m.alloc_request()
+    assert close(m.step([(rid, toks)], [list(range(40))]), oracle_logits(cfg, w, toks), F32)
+    m.close()
