@@ -776,17 +776,59 @@ def _arch_sizes():
     }
 
 
+def _risolorn_sizes():
+    """Risolorn stacks of the same width, head count, expert count and vocabulary as the Vamadra / Qwen3 stacks of `_arch_sizes`:
+    attention, delta rule, matrix memory, attention, every layer with routed experts."""
+    def ris(width, heads, kv, dim, chunk, experts, top, groups, keep, eff, vocab):
+        moe = {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": experts, "top": top, "groups": {"count": groups, "keep": keep}}}
+        att = {"type": "attention", "mlp": moe,
+               "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "mask": {"size": chunk}, "scale": dim ** -0.5,
+                         "rot": {"dims": dim // 2, "base": 500000.0, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+        dlt = {"type": "delta", "mlp": moe, "mixer": {"heads": heads, "kv_heads": heads // 2, "dim": dim, "vdim": dim, "conv": 4}}
+        mls = {"type": "mlstm", "mlp": moe, "mixer": {"heads": heads // 2, "dim": dim, "vdim": 2 * dim, "gate_cap": 15.0}}
+        return {"architecture": "Risolorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "logit_scale": 1.0,
+                "layers": [att, dlt, mls, att]}
+    return {"w2048": ris(2048, 16, 4, 128, 1024, 64, 6, 8, 4, 1408, 32768), "w1024": ris(1024, 8, 2, 64, 1024, 16, 2, 4, 2, 768, 32768)}
+
+
+def _measure_layered(vm, prompts, ctx, med, synthetic_prompt):
+    """prefill tok/s per prompt length and decode tok/s at batch 1 and 4 of a model on the layer-list host"""
+    res = {}
+    for T in prompts:
+        toks = synthetic_prompt(T)
+
+        def pre():
+            rid = vm.alloc_request()
+            vm.step([(rid, toks)])
+            vm.drop_request(rid)
+        res[f"prefill_{T}_tok_s"] = round(T / med(pre), 1)
+    for bs in (1, 4):
+        rids = [vm.alloc_request() for _ in range(bs)]
+        vm.step([(r, synthetic_prompt(ctx, i)) for i, r in enumerate(rids)])
+        vm.use_graph(False)  # one eager step to count the kernels a step launches (replayed graphs bypass the counter)
+        vm.launch_count(True)
+        vm.step([(r, [7]) for r in rids], sample=True)
+        res[f"decode_bs{bs}_launches_per_step"] = vm.launch_count()
+        vm.use_graph(True)
+        t = med(lambda: vm.step([(r, [7]) for r in rids], sample=True, logits=False))  # tokens back, as the Qwen3 arm
+        res[f"decode_bs{bs}_ctx{ctx}_tok_s"] = round(bs / t, 1)
+        for r in rids:
+            vm.drop_request(r)
+    return res
+
+
 def run_arch_compare(args):
-    """`--arch vamadra`: prefill and decode throughput of the Vamadra path beside the Qwen3 path at equal size.  Wall clock around
-    each public-API call (token ids from the host in, logits / token back out, stream synchronised), median of the repeats after
-    warm-up; between repeats nothing else runs on the GPU.  One JSON line."""
+    """`--arch vamadra`: prefill and decode throughput of the Vamadra path beside the Qwen3 path at equal size.  `--arch risolorn`:
+    the Risolorn path beside both.  Wall clock around each public-API call (token ids from the host in, logits / token back out,
+    stream synchronised), median of the repeats after warm-up; between repeats nothing else runs on the GPU.  One JSON line."""
     import torch
     from pegainfer_b200.model import ModelRuntimeConfig, Qwen3Model
     from pegainfer_b200.synthetic import iter_random_weights, synthetic_prompt
     from pegainfer_b200.vamadra import VamadraConfig, VamadraModel, iter_random_weights as vam_weights
     reps, warm = max(3, min(args.steps, 20)), max(3, min(args.warmup, 5))
     prompts, ctx, dec_steps = [512, 2048], 2048, 32
-    out = {"metric": "prefill_and_decode_tok_s", "arch": "vamadra", "beside": "qwen3", "dtype": "bf16", "data": "synthetic", "n_gpus": 1,
+    out = {"metric": "prefill_and_decode_tok_s", "arch": args.arch, "beside": "qwen3" if args.arch == "vamadra" else "vamadra, qwen3", "dtype": "bf16",
+           "data": "synthetic", "n_gpus": 1,
            "timing": "wall clock around the public API call incl. host->device ids and device->host result, stream synchronised", "sizes": {}}
 
     def med(f):
@@ -799,34 +841,20 @@ def run_arch_compare(args):
             ts.append(time.perf_counter() - t0)
         return statistics.median(ts)
 
+    pool_tokens = 4 * (ctx + 64) + max(prompts)
     for name, (vcfg_d, qcfg) in _arch_sizes().items():
         if args.arch_size and name not in args.arch_size.split(","):
             continue
         row = {}
+        if args.arch == "risolorn":
+            from pegainfer_b200.risolorn import RisolornConfig, RisolornModel, iter_random_weights as ris_weights
+            rcfg = RisolornConfig.from_dict(_risolorn_sizes()[name])
+            rm = RisolornModel(rcfg, ris_weights(rcfg, 0, "cuda"), max_tokens=pool_tokens, max_requests=5)
+            row["risolorn"] = _measure_layered(rm, prompts, ctx, med, synthetic_prompt)
+            rm.close()
         vcfg = VamadraConfig.from_dict(vcfg_d)
-        vm = VamadraModel(vcfg, vam_weights(vcfg, 0, "cuda"), max_tokens=4 * (ctx + 64) + max(prompts), max_requests=5)
-        res = {}
-        for T in prompts:
-            toks = synthetic_prompt(T)
-
-            def pre():
-                rid = vm.alloc_request()
-                vm.step([(rid, toks)])
-                vm.drop_request(rid)
-            res[f"prefill_{T}_tok_s"] = round(T / med(pre), 1)
-        for bs in (1, 4):
-            rids = [vm.alloc_request() for _ in range(bs)]
-            vm.step([(r, synthetic_prompt(ctx, i)) for i, r in enumerate(rids)])
-            vm.use_graph(False)  # one eager step to count the kernels a step launches (replayed graphs bypass the counter)
-            vm.launch_count(True)
-            vm.step([(r, [7]) for r in rids], sample=True)
-            res[f"decode_bs{bs}_launches_per_step"] = vm.launch_count()
-            vm.use_graph(True)
-            t = med(lambda: vm.step([(r, [7]) for r in rids], sample=True, logits=False))  # tokens back, as the Qwen3 arm
-            res[f"decode_bs{bs}_ctx{ctx}_tok_s"] = round(bs / t, 1)
-            for r in rids:
-                vm.drop_request(r)
-        row["vamadra"] = res
+        vm = VamadraModel(vcfg, vam_weights(vcfg, 0, "cuda"), max_tokens=pool_tokens, max_requests=5)
+        row["vamadra"] = _measure_layered(vm, prompts, ctx, med, synthetic_prompt)
         vm.close()
         qm = Qwen3Model(qcfg, iter_random_weights(qcfg, seed=0, device="cuda"),
                         ModelRuntimeConfig(enable_cuda_graph=True, fused=True, num_pages=(4 * (ctx + 64) + max(prompts)) // 16 + 8, max_batch=4))
@@ -870,8 +898,8 @@ def main():
     ap.add_argument("--weights", default="cpu", choices=["cpu", "cuda"],
                     help="cpu (default): the seed-0 CPU checkpoint the oracle fixtures were computed on; cuda: generated on "
                          "each GPU (fast; tuning sweeps only -- the parity key then reports a different checkpoint)")
-    ap.add_argument("--arch", default=None, choices=["vamadra"],
-                    help="instead of the headline workload: prefill / decode throughput of this design beside Qwen3 at equal size")
+    ap.add_argument("--arch", default=None, choices=["vamadra", "risolorn"],
+                    help="instead of the headline workload: prefill / decode throughput of this design beside the closest existing ones at equal size")
     ap.add_argument("--arch-size", default=None, help="with --arch: comma-separated subset of the sizes (w2048,w1024)")
     args = ap.parse_args()
     if args.arch:

@@ -9,16 +9,15 @@
 //
 // Step layout: entry e of the step owns rows [row0[e], row0[e] + len[e]) of every [tokens, features] buffer (a portion
 // of a prompt or one decoded token) and the state slot slot[e]; a slot's state is `state + slot * slot_stride` floats.
-// Sequence kernels: one CTA per (entry, head, slice of value columns); a thread owns one column of S in registers
-// (key size padded to the template's DK), tokens run one after the other, per block of kSeqTB tokens the unit keys /
-// queries and the gates are prepared by all warps in shared memory.  The matrix memory's normaliser n is one more
-// column with value 1.  Latency-bound per token (3 DK dependent FMAs per column, split over 4 partial sums).
+// Sequence kernels: one CTA per (entry, head, slice of value columns); a column of S lives in the registers of DK / 32
+// neighbouring lanes (key size padded to the template's DK), tokens run one after the other; per block of 32 tokens all
+// threads first bring q, k, v and the gate inputs into shared memory and turn them into unit vectors / gates.  The matrix
+// memory's normaliser n is one more column with value 1.  Latency-bound per token (96 dependent FMAs and two shuffle
+// reductions per thread).
 #include "common.cuh"
 #include "typed.cuh"
 
 namespace pk {
-
-constexpr int kSeqTB = 16;  // tokens prepared per block
 
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.f / (1.f + expf(-z)); }
 __device__ __forceinline__ float softplusf_(float z) { return z > 20.f ? z : log1pf(expf(z)); }
@@ -72,141 +71,175 @@ struct SeqArgs {
   const int *slot, *row0, *len;
   float* out;          // [tokens, H * vdim] fp32 read-out
   float* den;          // matrix memory: [tokens, H] divisor
-  int H, G, dim, vdim, cols_per_cta;
+  int H, G, dim, vdim;
   float cap;           // matrix memory: gate soft cap
 };
 
 // MODE 0: gated delta rule.  MODE 1: xLSTM matrix memory.
+// Thread layout: KS = DK / 32 neighbouring lanes share one state column, each holding 32 of its DK entries in registers
+// (entry (m * KS + ks) * 4 + e for m < 8, e < 4, so that the lanes' 16-byte reads of k / q from shared memory fall on
+// consecutive banks); the two dot products per token are finished with log2(KS) shuffles.  128 / KS columns per CTA; the
+// matrix memory's normaliser column rides in one more warp of the head's first CTA.
 template <typename E, int DK, int MODE>
-__global__ void __launch_bounds__(128) recurrent_seq_kernel(SeqArgs a) {
-  __shared__ __align__(16) float ks[kSeqTB][DK];
-  __shared__ __align__(16) float qs[kSeqTB][DK];
-  __shared__ float g0[kSeqTB], g1[kSeqTB];  // delta: decay, beta;  memory: log forget gate, log input gate
+__global__ void __launch_bounds__(160) recurrent_seq_kernel(SeqArgs a) {
+  constexpr int KS = DK / 32, COLS = 128 / KS, TB = DK <= 128 ? 32 : 16;
+  __shared__ __align__(16) float ks[TB][DK];
+  __shared__ __align__(16) float qs[TB][DK];
+  __shared__ float vs[TB][COLS];
+  __shared__ float g0[TB], g1[TB];  // delta: decay, write strength;  memory: log forget gate, log input gate
   pdl_wait();
   pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
   const int e = blockIdx.x, h = blockIdx.y, kvh = h / (a.H / a.G);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
   const int n = a.len[e], r0 = a.row0[e], dim = a.dim, vdim = a.vdim;
-  const int col = blockIdx.z * a.cols_per_cta + tid;
-  const int col_end = min(vdim, (int)(blockIdx.z + 1) * a.cols_per_cta);
-  // the normaliser column of the matrix memory rides in the first CTA of the head, after its value columns
-  const bool is_n = MODE == 1 && blockIdx.z == 0 && tid == min(a.cols_per_cta, vdim);
-  const bool is_v = tid < a.cols_per_cta && col < col_end;
+  const int cl = tid / KS, ksi = tid % KS;  // column inside the CTA, share of the key axis
+  const int col0 = blockIdx.z * COLS, col = col0 + cl;
+  const bool is_v = tid < 128 && col < vdim;
+  const bool is_n = MODE == 1 && blockIdx.z == 0 && tid >= 128 && tid < 128 + KS;
   float* base = a.state + (size_t)a.slot[e] * a.slot_stride;
-  float* S_g = base + (size_t)h * dim * vdim;               // [dim][vdim]
+  float* S_g = base + (size_t)h * dim * vdim;                      // [dim][vdim]
   float* n_g = base + (size_t)a.H * dim * vdim + (size_t)h * dim;  // matrix memory only
-  float* m_g = base + (size_t)a.H * dim * vdim + (size_t)a.H * dim + (size_t)h * (vdim + 1) + (is_v ? col : vdim);  // one copy per column: CTAs of a head never read what another one wrote
-  float S[DK];
+  // one copy of the running maximum per column: CTAs of a head never read what another one wrote
+  float* m_g = base + (size_t)a.H * dim * vdim + (size_t)a.H * dim + (size_t)h * (vdim + 1) + (is_v ? col : vdim);
+  float S[32];
 #pragma unroll
-  for (int i = 0; i < DK; ++i) S[i] = (i < dim) ? (is_v ? S_g[(size_t)i * vdim + col] : (is_n ? n_g[i] : 0.f)) : 0.f;
+  for (int j = 0; j < 32; ++j) {
+    const int i = ((j >> 2) * KS + ksi) * 4 + (j & 3);
+    S[j] = i < dim ? (is_v ? S_g[(size_t)i * vdim + col] : (is_n ? n_g[i] : 0.f)) : 0.f;
+  }
   float m = (MODE == 1 && (is_v || is_n)) ? m_g[0] : 0.f;
   const E* X = static_cast<const E*>(a.qkv);
   const float qscale = 1.f / sqrtf((float)dim);
-  for (int b0 = 0; b0 < n; b0 += kSeqTB) {
-    const int nb = min(kSeqTB, n - b0);
-    __syncthreads();
-    for (int tt = warp; tt < nb; tt += nw) {
-      const size_t row = (size_t)(r0 + b0 + tt);
-      const E* qr = X + row * a.ld + a.q_off + kvh * dim;
-      const E* kr = X + row * a.ld + a.k_off + kvh * dim;
-      float qq = 0.f, kk = 0.f;
-      for (int i = lane; i < dim; i += 32) {
-        const float qv = to_f(qr[i]), kv = to_f(kr[i]);
-        qq = fmaf(qv, qv, qq);
-        kk = fmaf(kv, kv, kk);
+  const size_t out_ld = (size_t)a.H * vdim;
+  for (int b0 = 0; b0 < n; b0 += TB) {
+    const int nb = min(TB, n - b0);
+    __syncthreads();  // the previous block's readers are done
+    // 1. raw q, k, v and gate inputs of the block's tokens (independent loads, many in flight)
+    const E* Xb = X + (size_t)(r0 + b0) * a.ld;
+#pragma unroll 4
+    for (int i = tid; i < nb * DK; i += blockDim.x) {
+      const int tt = i / DK, d = i % DK;
+      const E* row = Xb + (size_t)tt * a.ld;
+      qs[tt][d] = d < dim ? to_f(row[a.q_off + kvh * dim + d]) : 0.f;
+      ks[tt][d] = d < dim ? to_f(row[a.k_off + kvh * dim + d]) : 0.f;
+    }
+#pragma unroll 4
+    for (int i = tid; i < nb * COLS; i += blockDim.x) {
+      const int tt = i / COLS, c = i % COLS;
+      vs[tt][c] = col0 + c < vdim ? to_f(Xb[(size_t)tt * a.ld + a.v_off + h * vdim + col0 + c]) : 0.f;
+    }
+    if (tid < nb) {
+      const size_t row = (size_t)(r0 + b0 + tid);
+      const float za = a.z[row * a.ldz + a.za_off + h], zb = a.z[row * a.ldz + a.zb_off + h];
+      if (MODE == 0) {  // za: decay projection, zb: write-strength projection
+        g0[tid] = expf(-expf(a.p0[h]) * softplusf_(za + a.p1[h]));
+        g1[tid] = sigmoidf_(zb);
+      } else {  // za: forget gate, zb: input gate
+        g0[tid] = logsigmoidf_(a.cap * tanhf((za + a.p1[h]) / a.cap));
+        g1[tid] = a.cap * tanhf((zb + a.p0[h]) / a.cap);
       }
+    }
+    __syncthreads();
+    // 2. unit vectors (delta rule) and the query's scale
+    for (int tt = warp; tt < nb; tt += nw) {
       float qf = qscale, kf = 1.f;
       if (MODE == 0) {
+        float qq = 0.f, kk = 0.f;
+        for (int i = lane; i < DK; i += 32) {
+          qq = fmaf(qs[tt][i], qs[tt][i], qq);
+          kk = fmaf(ks[tt][i], ks[tt][i], kk);
+        }
         qq = warp_sum(qq);
         kk = warp_sum(kk);
         qf = qscale / sqrtf(qq + 1e-6f);
         kf = 1.f / sqrtf(kk + 1e-6f);
       }
       for (int i = lane; i < DK; i += 32) {
-        qs[tt][i] = i < dim ? to_f(qr[i]) * qf : 0.f;
-        ks[tt][i] = i < dim ? to_f(kr[i]) * kf : 0.f;
-      }
-      if (lane == 0) {
-        const float za = a.z[row * a.ldz + a.za_off + h], zb = a.z[row * a.ldz + a.zb_off + h];
-        if (MODE == 0) {  // za: decay projection, zb: write-strength projection
-          g0[tt] = expf(-expf(a.p0[h]) * softplusf_(za + a.p1[h]));
-          g1[tt] = sigmoidf_(zb);
-        } else {  // za: forget gate, zb: input gate
-          g0[tt] = logsigmoidf_(a.cap * tanhf((za + a.p1[h]) / a.cap));
-          g1[tt] = a.cap * tanhf((zb + a.p0[h]) / a.cap);
-        }
+        qs[tt][i] *= qf;
+        if (MODE == 0) ks[tt][i] *= kf;
       }
     }
     __syncthreads();
-    if (!is_v && !is_n) continue;
+    if (warp >= 4 && !(MODE == 1 && blockIdx.z == 0)) continue;  // the extra warp only carries the normaliser
+    // 3. the recurrence, token by token (whole warps run it: the shuffles below need every lane)
     for (int tt = 0; tt < nb; ++tt) {
       const size_t row = (size_t)(r0 + b0 + tt);
-      const float vt = is_v ? to_f(X[row * a.ld + a.v_off + h * vdim + col]) : 1.f;
+      const float vt = tid < 128 ? vs[tt][cl] : 1.f;
+      const float4* k4p = reinterpret_cast<const float4*>(&ks[tt][0]) + ksi;
+      const float4* q4p = reinterpret_cast<const float4*>(&qs[tt][0]) + ksi;
       float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
       if (MODE == 0) {
         const float g = g0[tt], beta = g1[tt];
         float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
 #pragma unroll
-        for (int i = 0; i < DK; i += 4) {
-          const float4 k4 = *reinterpret_cast<const float4*>(&ks[tt][i]);
-          S[i] *= g;
-          S[i + 1] *= g;
-          S[i + 2] *= g;
-          S[i + 3] *= g;
-          c0 = fmaf(S[i], k4.x, c0);
-          c1 = fmaf(S[i + 1], k4.y, c1);
-          c2 = fmaf(S[i + 2], k4.z, c2);
-          c3 = fmaf(S[i + 3], k4.w, c3);
+        for (int mi = 0; mi < 8; ++mi) {
+          const float4 k4 = k4p[mi * KS];
+          S[mi * 4] *= g;
+          S[mi * 4 + 1] *= g;
+          S[mi * 4 + 2] *= g;
+          S[mi * 4 + 3] *= g;
+          c0 = fmaf(S[mi * 4], k4.x, c0);
+          c1 = fmaf(S[mi * 4 + 1], k4.y, c1);
+          c2 = fmaf(S[mi * 4 + 2], k4.z, c2);
+          c3 = fmaf(S[mi * 4 + 3], k4.w, c3);
         }
-        const float u = beta * (vt - ((c0 + c1) + (c2 + c3)));
+        float kv = (c0 + c1) + (c2 + c3);
 #pragma unroll
-        for (int i = 0; i < DK; i += 4) {
-          const float4 k4 = *reinterpret_cast<const float4*>(&ks[tt][i]);
-          const float4 q4 = *reinterpret_cast<const float4*>(&qs[tt][i]);
-          S[i] = fmaf(k4.x, u, S[i]);
-          S[i + 1] = fmaf(k4.y, u, S[i + 1]);
-          S[i + 2] = fmaf(k4.z, u, S[i + 2]);
-          S[i + 3] = fmaf(k4.w, u, S[i + 3]);
-          o0 = fmaf(S[i], q4.x, o0);
-          o1 = fmaf(S[i + 1], q4.y, o1);
-          o2 = fmaf(S[i + 2], q4.z, o2);
-          o3 = fmaf(S[i + 3], q4.w, o3);
+        for (int o = 1; o < KS; o <<= 1) kv += __shfl_xor_sync(0xffffffffu, kv, o);
+        const float u = beta * (vt - kv);
+#pragma unroll
+        for (int mi = 0; mi < 8; ++mi) {
+          const float4 k4 = k4p[mi * KS];
+          const float4 q4 = q4p[mi * KS];
+          S[mi * 4] = fmaf(k4.x, u, S[mi * 4]);
+          S[mi * 4 + 1] = fmaf(k4.y, u, S[mi * 4 + 1]);
+          S[mi * 4 + 2] = fmaf(k4.z, u, S[mi * 4 + 2]);
+          S[mi * 4 + 3] = fmaf(k4.w, u, S[mi * 4 + 3]);
+          o0 = fmaf(S[mi * 4], q4.x, o0);
+          o1 = fmaf(S[mi * 4 + 1], q4.y, o1);
+          o2 = fmaf(S[mi * 4 + 2], q4.z, o2);
+          o3 = fmaf(S[mi * 4 + 3], q4.w, o3);
         }
-        a.out[row * ((size_t)a.H * vdim) + h * vdim + col] = (o0 + o1) + (o2 + o3);
+        float o = (o0 + o1) + (o2 + o3);
+#pragma unroll
+        for (int s = 1; s < KS; s <<= 1) o += __shfl_xor_sync(0xffffffffu, o, s);
+        if (is_v && ksi == 0) a.out[row * out_ld + h * vdim + col] = o;
       } else {
         const float f = g0[tt], ig = g1[tt];
         const float mn = fmaxf(f + m, ig);
         const float fa = expf(f + m - mn), wb = expf(ig - mn) * vt;
         m = mn;
 #pragma unroll
-        for (int i = 0; i < DK; i += 4) {
-          const float4 k4 = *reinterpret_cast<const float4*>(&ks[tt][i]);
-          const float4 q4 = *reinterpret_cast<const float4*>(&qs[tt][i]);
-          S[i] = fmaf(k4.x, wb, fa * S[i]);
-          S[i + 1] = fmaf(k4.y, wb, fa * S[i + 1]);
-          S[i + 2] = fmaf(k4.z, wb, fa * S[i + 2]);
-          S[i + 3] = fmaf(k4.w, wb, fa * S[i + 3]);
-          o0 = fmaf(S[i], q4.x, o0);
-          o1 = fmaf(S[i + 1], q4.y, o1);
-          o2 = fmaf(S[i + 2], q4.z, o2);
-          o3 = fmaf(S[i + 3], q4.w, o3);
+        for (int mi = 0; mi < 8; ++mi) {
+          const float4 k4 = k4p[mi * KS];
+          const float4 q4 = q4p[mi * KS];
+          S[mi * 4] = fmaf(k4.x, wb, fa * S[mi * 4]);
+          S[mi * 4 + 1] = fmaf(k4.y, wb, fa * S[mi * 4 + 1]);
+          S[mi * 4 + 2] = fmaf(k4.z, wb, fa * S[mi * 4 + 2]);
+          S[mi * 4 + 3] = fmaf(k4.w, wb, fa * S[mi * 4 + 3]);
+          o0 = fmaf(S[mi * 4], q4.x, o0);
+          o1 = fmaf(S[mi * 4 + 1], q4.y, o1);
+          o2 = fmaf(S[mi * 4 + 2], q4.z, o2);
+          o3 = fmaf(S[mi * 4 + 3], q4.w, o3);
         }
-        const float o = (o0 + o1) + (o2 + o3);
-        if (is_v) a.out[row * ((size_t)a.H * vdim) + h * vdim + col] = o;
-        else a.den[row * a.H + h] = fmaxf(fabsf(o), expf(-mn)) + 1e-6f;
+        float o = (o0 + o1) + (o2 + o3);
+#pragma unroll
+        for (int s = 1; s < KS; s <<= 1) o += __shfl_xor_sync(0xffffffffu, o, s);
+        if (is_v && ksi == 0) a.out[row * out_ld + h * vdim + col] = o;
+        else if (is_n && ksi == 0) a.den[row * a.H + h] = fmaxf(fabsf(o), expf(-mn)) + 1e-6f;
       }
     }
   }
-  if (is_v) {
+  if (is_v || is_n) {
 #pragma unroll
-    for (int i = 0; i < DK; ++i)
-      if (i < dim) S_g[(size_t)i * vdim + col] = S[i];
-    if (MODE == 1) m_g[0] = m;
-  } else if (is_n) {
-#pragma unroll
-    for (int i = 0; i < DK; ++i)
-      if (i < dim) n_g[i] = S[i];
-    m_g[0] = m;
+    for (int j = 0; j < 32; ++j) {
+      const int i = ((j >> 2) * KS + ksi) * 4 + (j & 3);
+      if (i < dim) {
+        if (is_v) S_g[(size_t)i * vdim + col] = S[j];
+        else n_g[i] = S[j];
+      }
+    }
+    if (MODE == 1 && ksi == 0) m_g[0] = m;
   }
 }
 
@@ -241,24 +274,14 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* 
 
 template <typename E, int MODE>
 static int launch_seq(const SeqArgs& a, int entries, cudaStream_t st) {
-  // columns per CTA: whole warps; short steps (decoding) spread a head over more CTAs
-  int cols = a.vdim <= 32 ? a.vdim : (a.vdim + 1) / 2;
-  if (cols > 96) cols = 96;
-  if (cols > 32) cols = (cols + 31) / 32 * 32;
-  if (cols > a.vdim) cols = a.vdim;
-  SeqArgs b = a;
-  b.cols_per_cta = cols;
-  const int threads = std::min(128, (cols + (MODE == 1 ? 1 : 0) + 31) / 32 * 32);
-  if (cols + (MODE == 1 ? 1 : 0) > threads) {  // the extra column does not fit: one warp less of value columns
-    b.cols_per_cta = cols = threads - 32;
-  }
-  const dim3 grid(entries, a.H, (a.vdim + cols - 1) / cols);
-  const int dk = a.dim <= 32 ? 32 : a.dim <= 64 ? 64 : a.dim <= 128 ? 128 : 256;
   if (a.dim > 256) return -2;
-  if (dk == 32) launch(recurrent_seq_kernel<E, 32, MODE>, grid, dim3(threads), 0, st, true, b);
-  else if (dk == 64) launch(recurrent_seq_kernel<E, 64, MODE>, grid, dim3(threads), 0, st, true, b);
-  else if (dk == 128) launch(recurrent_seq_kernel<E, 128, MODE>, grid, dim3(threads), 0, st, true, b);
-  else launch(recurrent_seq_kernel<E, 256, MODE>, grid, dim3(threads), 0, st, true, b);
+  const int dk = a.dim <= 32 ? 32 : a.dim <= 64 ? 64 : a.dim <= 128 ? 128 : 256;
+  const int cols = 128 / (dk / 32);
+  const dim3 grid(entries, a.H, (a.vdim + cols - 1) / cols), block(MODE == 1 ? 160 : 128);
+  if (dk == 32) launch(recurrent_seq_kernel<E, 32, MODE>, grid, block, 0, st, true, a);
+  else if (dk == 64) launch(recurrent_seq_kernel<E, 64, MODE>, grid, block, 0, st, true, a);
+  else if (dk == 128) launch(recurrent_seq_kernel<E, 128, MODE>, grid, block, 0, st, true, a);
+  else launch(recurrent_seq_kernel<E, 256, MODE>, grid, block, 0, st, true, a);
   return (int)cudaGetLastError();
 }
 
@@ -297,7 +320,7 @@ extern "C" int pk_gated_delta_seq(const void* qkv, int ld, int q_off, int k_off,
                                   const int* len, float* out, int heads, int kv_heads, int dim, int vdim, int entries, int f32, pk_stream st) {
   if (!seq_args_ok(qkv, z, a_log, dt_bias, state, slot, row0, len, out, heads, kv_heads, dim, vdim, entries)) return -1;
   SeqArgs a{qkv, ld, q_off, k_off, v_off, z, ldz, decay_off, beta_off, a_log, dt_bias, state, slot_stride, slot, row0, len, out, nullptr,
-            heads, kv_heads, dim, vdim, 0, 0.f};
+            heads, kv_heads, dim, vdim, 0.f};
   return f32 ? launch_seq<float, 0>(a, entries, st) : launch_seq<bf16, 0>(a, entries, st);
 }
 
@@ -307,7 +330,7 @@ extern "C" int pk_mlstm_seq(const void* qkv, int ld, int q_off, int k_off, int v
                             pk_stream st) {
   if (!seq_args_ok(qkv, z, input_bias, forget_bias, state, slot, row0, len, out, heads, heads, dim, vdim, entries) || !den || !(cap > 0.f)) return -1;
   SeqArgs a{qkv, ld, q_off, k_off, v_off, z, ldz, forget_off, input_off, input_bias, forget_bias, state, slot_stride, slot, row0, len, out, den,
-            heads, heads, dim, vdim, 0, cap};
+            heads, heads, dim, vdim, cap};
   return f32 ? launch_seq<float, 1>(a, entries, st) : launch_seq<bf16, 1>(a, entries, st);
 }
 
