@@ -29,7 +29,7 @@ __global__ void gqa_rope_append_kernel(const E* __restrict__ qkv, int ld, const 
   const E* row = qkv + (size_t)t * ld;
   const int nq = H * dim, nk = G * dim, nv = G * vdim, half = dims >> 1;
   E* slot = cache + (size_t)pages[page_off[req[t]] + p / page_size] * page_stride + (size_t)(p % page_size) * (nk + nv);
-  for (int e = threadIdx.x; e < nq + nk + nv; e += blockDim.x) {
+  for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < nq + nk + nv; e += gridDim.y * blockDim.x) {
     float v = to_f(row[e]) + (bias ? to_f(bias[e]) : 0.f);
     if (e < nq + nk) {
       const int d = (e < nq ? e : e - nq) % dim;
@@ -132,8 +132,9 @@ __global__ void __launch_bounds__(kGqaWarps * 32) gqa_attention_kernel(const E* 
 
 // ---- tensor cores (bf16): one CTA = 64 consecutive rows of the step (4 warps x 16 rows) for one query head.  Rows of a
 // tile may belong to several requests: the tile walks each request's visible key range in 64-key blocks with the other
-// rows masked.  dim, vdim multiples of 16 up to 128.  K and V blocks are staged in shared memory; S = Q K^T and O += P V
-// with mma.sync m16n8k16, P rounded to bf16 for the second product, statistics in fp32.
+// rows masked.  dim, vdim multiples of 16 up to 128.  K and V blocks go through a two-stage cp.async ring in shared memory (the
+// next block's copy overlaps this block's products); S = Q K^T and O += P V with mma.sync m16n8k16, P rounded to bf16 for the
+// second product, statistics in fp32.
 constexpr int kAmRows = 64, kAmKeys = 64;
 
 template <int DQ, int DV>
@@ -143,8 +144,9 @@ __global__ void __launch_bounds__(128) gqa_attention_mma_kernel(const bf16* __re
                                                                bf16* __restrict__ out, long page_stride, int page_size, int T, int H, int G,
                                                                float scale, int chunk) {
   constexpr int LDK = DQ + 8, LDV = DV + 8;
-  __shared__ __align__(16) bf16 Ks[kAmKeys * LDK];
-  __shared__ __align__(16) bf16 Vs[kAmKeys * LDV];
+  extern __shared__ __align__(16) unsigned char am_smem[];  // two stages of [keys][LDK] K and [keys][LDV] V
+  bf16* const Ks0 = reinterpret_cast<bf16*>(am_smem);
+  bf16* const Vs0 = Ks0 + 2 * kAmKeys * LDK;
   __shared__ int s_req[kAmRows], s_pos[kAmRows];
   pdl_wait();
   pdl_launch_dependents();  // the next kernel may start its launch; it waits for this grid to finish before it reads
@@ -184,21 +186,33 @@ __global__ void __launch_bounds__(128) gqa_attention_mma_kernel(const bf16* __re
     const int p_min = s_pos[r_first], p_max = s_pos[r_last];
     const int k_lo = chunk > 0 ? (p_min / chunk) * chunk : 0;
     const int* pg = pages + page_off[rq];
-    for (int k0 = k_lo - (k_lo % kAmKeys); k0 <= p_max; k0 += kAmKeys) {
-      __syncthreads();  // the previous block's readers are done
+    // stage `buf` <- keys k0 .. k0 + 63 of this request (cp.async; rows outside [k_lo, p_max] are zero-filled)
+    auto load = [&](int k0, int buf) {
+      bf16* Kd = Ks0 + buf * kAmKeys * LDK;
+      bf16* Vd = Vs0 + buf * kAmKeys * LDV;
       for (int c = tid; c < kAmKeys * (DQ / 8); c += 128) {
         const int r = c / (DQ / 8), cc = (c % (DQ / 8)) * 8, j = k0 + r;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (j <= p_max && j >= k_lo) v = *reinterpret_cast<const uint4*>(cache + (size_t)pg[j / page_size] * page_stride + (size_t)(j % page_size) * tok + g * DQ + cc);
-        *reinterpret_cast<uint4*>(&Ks[r * LDK + cc]) = v;
+        if (j <= p_max && j >= k_lo) cp_async16(&Kd[r * LDK + cc], cache + (size_t)pg[j / page_size] * page_stride + (size_t)(j % page_size) * tok + g * DQ + cc);
+        else *reinterpret_cast<uint4*>(&Kd[r * LDK + cc]) = make_uint4(0, 0, 0, 0);
       }
       for (int c = tid; c < kAmKeys * (DV / 8); c += 128) {
         const int r = c / (DV / 8), cc = (c % (DV / 8)) * 8, j = k0 + r;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (j <= p_max && j >= k_lo) v = *reinterpret_cast<const uint4*>(cache + (size_t)pg[j / page_size] * page_stride + (size_t)(j % page_size) * tok + G * DQ + g * DV + cc);
-        *reinterpret_cast<uint4*>(&Vs[r * LDV + cc]) = v;
+        if (j <= p_max && j >= k_lo)
+          cp_async16(&Vd[r * LDV + cc], cache + (size_t)pg[j / page_size] * page_stride + (size_t)(j % page_size) * tok + G * DQ + g * DV + cc);
+        else *reinterpret_cast<uint4*>(&Vd[r * LDV + cc]) = make_uint4(0, 0, 0, 0);
       }
-      __syncthreads();
+      cp_async_commit();
+    };
+    const int k_first = k_lo - (k_lo % kAmKeys);
+    __syncthreads();  // the previous request's readers are done with both stages
+    load(k_first, 0);
+    for (int k0 = k_first, it = 0; k0 <= p_max; k0 += kAmKeys, ++it) {
+      const int buf = it & 1;
+      cp_async_wait_all();
+      __syncthreads();  // this block has landed, and nobody reads the other stage any more
+      if (k0 + kAmKeys <= p_max) load(k0 + kAmKeys, buf ^ 1);  // overlaps the products below
+      const bf16* Ks = Ks0 + buf * kAmKeys * LDK;
+      const bf16* Vs = Vs0 + buf * kAmKeys * LDV;
       const bool on_a = req_a == rq, on_b = req_b == rq;
       if (!__any_sync(0xffffffffu, on_a || on_b)) continue;  // warp-uniform: the tensor-core instructions below need all 32 lanes
       // S = Q K^T: 16 rows x 64 keys per warp
@@ -287,7 +301,13 @@ __global__ void __launch_bounds__(128) gqa_attention_mma_kernel(const bf16* __re
 template <int DQ, int DV>
 static void launch_gqa_mma(const bf16* q, const bf16* cache, const bf16* sink, const int* pos, const int* req, const int* page_off, const int* pages,
                            bf16* out, long page_stride, int page_size, int T, int H, int G, float scale, int chunk, cudaStream_t st) {
-  launch(gqa_attention_mma_kernel<DQ, DV>, dim3((T + kAmRows - 1) / kAmRows, H), dim3(128), 0, st, true, q, cache, sink, pos, req, page_off, pages, out,
+  const size_t smem = (size_t)2 * kAmKeys * (DQ + 8 + DV + 8) * sizeof(bf16);
+  static bool attr_set = false;  // per template instance
+  if (!attr_set) {
+    cudaFuncSetAttribute(gqa_attention_mma_kernel<DQ, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attr_set = true;
+  }
+  launch(gqa_attention_mma_kernel<DQ, DV>, dim3((T + kAmRows - 1) / kAmRows, H), dim3(128), smem, st, true, q, cache, sink, pos, req, page_off, pages, out,
          page_stride, page_size, T, H, G, scale, chunk);
 }
 
@@ -301,11 +321,14 @@ extern "C" int pk_gqa_rope_append(const void* qkv, int ld, const void* bias, con
   if (!qkv || !positions || !req || !page_off || !pages || !q_out || !cache || tokens <= 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads ||
       dim <= 0 || vdim <= 0 || dims < 0 || dims > dim || (dims & 1) || (dims > 0 && !freq) || page_size <= 0)
     return -1;
+  // few tokens (decoding): a token's features are spread over several CTAs
+  const int n_all = heads * dim + kv_heads * (dim + vdim);
+  const dim3 grid(tokens, tokens >= 128 ? 1 : std::min((n_all + 255) / 256, 16));
   if (f32)
-    launch(gqa_rope_append_kernel<float>, dim3(tokens), dim3(256), 0, st, true, (const float*)qkv, ld, (const float*)bias, positions, req, page_off, pages,
+    launch(gqa_rope_append_kernel<float>, grid, dim3(256), 0, st, true, (const float*)qkv, ld, (const float*)bias, positions, req, page_off, pages,
            (float*)q_out, (float*)cache, page_stride, page_size, heads, kv_heads, dim, vdim, dims, interleaved, freq, mag);
   else
-    launch(gqa_rope_append_kernel<bf16>, dim3(tokens), dim3(256), 0, st, true, (const bf16*)qkv, ld, (const bf16*)bias, positions, req, page_off, pages,
+    launch(gqa_rope_append_kernel<bf16>, grid, dim3(256), 0, st, true, (const bf16*)qkv, ld, (const bf16*)bias, positions, req, page_off, pages,
            (bf16*)q_out, (bf16*)cache, page_stride, page_size, heads, kv_heads, dim, vdim, dims, interleaved, freq, mag);
   return (int)cudaGetLastError();
 }
