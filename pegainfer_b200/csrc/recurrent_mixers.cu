@@ -9,11 +9,11 @@
 //
 // Step layout: entry e of the step owns rows [row0[e], row0[e] + len[e]) of every [tokens, features] buffer (a portion
 // of a prompt or one decoded token) and the state slot slot[e]; a slot's state is `state + slot * slot_stride` floats.
-// Sequence kernels: one CTA per (entry, head, slice of value columns); a column of S lives in the registers of DK / 32
+// Sequence kernels: one CTA per (entry, head, slice of value columns); a column of S lives in the registers of DK / 16
 // neighbouring lanes (key size padded to the template's DK), tokens run one after the other; per block of 32 tokens all
 // threads first bring q, k, v and the gate inputs into shared memory and turn them into unit vectors / gates.  The matrix
-// memory's normaliser n is one more column with value 1.  Latency-bound per token (96 dependent FMAs and two shuffle
-// reductions per thread).
+// memory's normaliser n is one more column with value 1.  Latency-bound per token (48 FMAs and two shuffle reductions per
+// thread, one warp per scheduler).
 #include "common.cuh"
 #include "typed.cuh"
 
@@ -76,13 +76,13 @@ struct SeqArgs {
 };
 
 // MODE 0: gated delta rule.  MODE 1: xLSTM matrix memory.
-// Thread layout: KS = DK / 32 neighbouring lanes share one state column, each holding 32 of its DK entries in registers
-// (entry (m * KS + ks) * 4 + e for m < 8, e < 4, so that the lanes' 16-byte reads of k / q from shared memory fall on
+// Thread layout: KS = DK / 16 neighbouring lanes share one state column, each holding 16 of its DK entries in registers
+// (entry (m * KS + ks) * 4 + e for m < 4, e < 4, so that the lanes' 16-byte reads of k / q from shared memory fall on
 // consecutive banks); the two dot products per token are finished with log2(KS) shuffles.  128 / KS columns per CTA; the
 // matrix memory's normaliser column rides in one more warp of the head's first CTA.
 template <typename E, int DK, int MODE>
 __global__ void __launch_bounds__(160) recurrent_seq_kernel(SeqArgs a) {
-  constexpr int KS = DK / 32, COLS = 128 / KS, TB = DK <= 128 ? 32 : 16;
+  constexpr int KS = DK / 16, COLS = 128 / KS, TB = DK <= 128 ? 32 : 16, NS = 16;  // NS state entries per thread
   __shared__ __align__(16) float ks[TB][DK];
   __shared__ __align__(16) float qs[TB][DK];
   __shared__ float vs[TB][COLS];
@@ -101,9 +101,9 @@ __global__ void __launch_bounds__(160) recurrent_seq_kernel(SeqArgs a) {
   float* n_g = base + (size_t)a.H * dim * vdim + (size_t)h * dim;  // matrix memory only
   // one copy of the running maximum per column: CTAs of a head never read what another one wrote
   float* m_g = base + (size_t)a.H * dim * vdim + (size_t)a.H * dim + (size_t)h * (vdim + 1) + (is_v ? col : vdim);
-  float S[32];
+  float S[NS];
 #pragma unroll
-  for (int j = 0; j < 32; ++j) {
+  for (int j = 0; j < NS; ++j) {
     const int i = ((j >> 2) * KS + ksi) * 4 + (j & 3);
     S[j] = i < dim ? (is_v ? S_g[(size_t)i * vdim + col] : (is_n ? n_g[i] : 0.f)) : 0.f;
   }
@@ -116,15 +116,45 @@ __global__ void __launch_bounds__(160) recurrent_seq_kernel(SeqArgs a) {
     __syncthreads();  // the previous block's readers are done
     // 1. raw q, k, v and gate inputs of the block's tokens (independent loads, many in flight)
     const E* Xb = X + (size_t)(r0 + b0) * a.ld;
+    bool staged = false;
+    if constexpr (sizeof(E) == 2) {
+      // 16-byte pieces of 8 bf16 when every row slice starts on a 16-byte boundary
+      const int qo = a.q_off + kvh * dim, ko = a.k_off + kvh * dim, vo = a.v_off + h * vdim + col0;
+      if (((a.ld | qo | ko | vo | dim | vdim) & 7) == 0 && (reinterpret_cast<uintptr_t>(X) & 15) == 0) {
+        staged = true;
+        constexpr int PR = DK / 8;
+        for (int i = tid; i < nb * PR; i += blockDim.x) {
+          const int tt = i / PR, d0 = (i % PR) * 8;
+          const E* row = Xb + (size_t)tt * a.ld;
+          uint4 qv = make_uint4(0, 0, 0, 0), kv = qv;
+          if (d0 < dim) {
+            qv = *reinterpret_cast<const uint4*>(row + qo + d0);
+            kv = *reinterpret_cast<const uint4*>(row + ko + d0);
+          }
+          *reinterpret_cast<float4*>(&qs[tt][d0]) = make_float4(bf16_lo(qv.x), bf16_hi(qv.x), bf16_lo(qv.y), bf16_hi(qv.y));
+          *reinterpret_cast<float4*>(&qs[tt][d0 + 4]) = make_float4(bf16_lo(qv.z), bf16_hi(qv.z), bf16_lo(qv.w), bf16_hi(qv.w));
+          *reinterpret_cast<float4*>(&ks[tt][d0]) = make_float4(bf16_lo(kv.x), bf16_hi(kv.x), bf16_lo(kv.y), bf16_hi(kv.y));
+          *reinterpret_cast<float4*>(&ks[tt][d0 + 4]) = make_float4(bf16_lo(kv.z), bf16_hi(kv.z), bf16_lo(kv.w), bf16_hi(kv.w));
+        }
+        constexpr int PV = COLS / 8;
+        for (int i = tid; i < nb * PV; i += blockDim.x) {
+          const int tt = i / PV, c0 = (i % PV) * 8;
+          uint4 vv = make_uint4(0, 0, 0, 0);
+          if (col0 + c0 < vdim) vv = *reinterpret_cast<const uint4*>(Xb + (size_t)tt * a.ld + vo + c0);
+          vs[tt][c0] = bf16_lo(vv.x), vs[tt][c0 + 1] = bf16_hi(vv.x), vs[tt][c0 + 2] = bf16_lo(vv.y), vs[tt][c0 + 3] = bf16_hi(vv.y);
+          vs[tt][c0 + 4] = bf16_lo(vv.z), vs[tt][c0 + 5] = bf16_hi(vv.z), vs[tt][c0 + 6] = bf16_lo(vv.w), vs[tt][c0 + 7] = bf16_hi(vv.w);
+        }
+      }
+    }
 #pragma unroll 4
-    for (int i = tid; i < nb * DK; i += blockDim.x) {
+    for (int i = staged ? nb * DK : tid; i < nb * DK; i += blockDim.x) {
       const int tt = i / DK, d = i % DK;
       const E* row = Xb + (size_t)tt * a.ld;
       qs[tt][d] = d < dim ? to_f(row[a.q_off + kvh * dim + d]) : 0.f;
       ks[tt][d] = d < dim ? to_f(row[a.k_off + kvh * dim + d]) : 0.f;
     }
 #pragma unroll 4
-    for (int i = tid; i < nb * COLS; i += blockDim.x) {
+    for (int i = staged ? nb * COLS : tid; i < nb * COLS; i += blockDim.x) {
       const int tt = i / COLS, c = i % COLS;
       vs[tt][c] = col0 + c < vdim ? to_f(Xb[(size_t)tt * a.ld + a.v_off + h * vdim + col0 + c]) : 0.f;
     }
@@ -172,7 +202,7 @@ __global__ void __launch_bounds__(160) recurrent_seq_kernel(SeqArgs a) {
         const float g = g0[tt], beta = g1[tt];
         float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
 #pragma unroll
-        for (int mi = 0; mi < 8; ++mi) {
+        for (int mi = 0; mi < NS / 4; ++mi) {
           const float4 k4 = k4p[mi * KS];
           S[mi * 4] *= g;
           S[mi * 4 + 1] *= g;
@@ -188,7 +218,7 @@ __global__ void __launch_bounds__(160) recurrent_seq_kernel(SeqArgs a) {
         for (int o = 1; o < KS; o <<= 1) kv += __shfl_xor_sync(0xffffffffu, kv, o);
         const float u = beta * (vt - kv);
 #pragma unroll
-        for (int mi = 0; mi < 8; ++mi) {
+        for (int mi = 0; mi < NS / 4; ++mi) {
           const float4 k4 = k4p[mi * KS];
           const float4 q4 = q4p[mi * KS];
           S[mi * 4] = fmaf(k4.x, u, S[mi * 4]);
@@ -210,7 +240,7 @@ __global__ void __launch_bounds__(160) recurrent_seq_kernel(SeqArgs a) {
         const float fa = expf(f + m - mn), wb = expf(ig - mn) * vt;
         m = mn;
 #pragma unroll
-        for (int mi = 0; mi < 8; ++mi) {
+        for (int mi = 0; mi < NS / 4; ++mi) {
           const float4 k4 = k4p[mi * KS];
           const float4 q4 = q4p[mi * KS];
           S[mi * 4] = fmaf(k4.x, wb, fa * S[mi * 4]);
@@ -232,7 +262,7 @@ __global__ void __launch_bounds__(160) recurrent_seq_kernel(SeqArgs a) {
   }
   if (is_v || is_n) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
+    for (int j = 0; j < NS; ++j) {
       const int i = ((j >> 2) * KS + ksi) * 4 + (j & 3);
       if (i < dim) {
         if (is_v) S_g[(size_t)i * vdim + col] = S[j];
@@ -276,7 +306,7 @@ template <typename E, int MODE>
 static int launch_seq(const SeqArgs& a, int entries, cudaStream_t st) {
   if (a.dim > 256) return -2;
   const int dk = a.dim <= 32 ? 32 : a.dim <= 64 ? 64 : a.dim <= 128 ? 128 : 256;
-  const int cols = 128 / (dk / 32);
+  const int cols = 128 / (dk / 16);
   const dim3 grid(entries, a.H, (a.vdim + cols - 1) / cols), block(MODE == 1 ? 160 : 128);
   if (dk == 32) launch(recurrent_seq_kernel<E, 32, MODE>, grid, block, 0, st, true, a);
   else if (dk == 64) launch(recurrent_seq_kernel<E, 64, MODE>, grid, block, 0, st, true, a);
