@@ -192,6 +192,7 @@ __global__ void __launch_bounds__(160) recurrent_seq_kernel(SeqArgs a) {
     __syncthreads();
     if (warp >= 4 && !(MODE == 1 && blockIdx.z == 0)) continue;  // the extra warp only carries the normaliser
     // 3. the recurrence, token by token (whole warps run it: the shuffles below need every lane)
+#pragma unroll 2
     for (int tt = 0; tt < nb; ++tt) {
       const size_t row = (size_t)(r0 + b0 + tt);
       const float vt = tid < 128 ? vs[tt][cl] : 1.f;

@@ -45,19 +45,24 @@ class MixerConfig:
         if kind not in MIXER_KINDS:
             raise ValueError(f"unknown mixer type {kind!r}")
         heads, dim, vdim = int(d["heads"]), int(d["dim"]), int(d["vdim"])
-        if kind == "attention":
-            return MixerConfig(kind, heads, dim, vdim, int(d["kv_heads"]), float(d["scale"]), int(d["mask"]["size"]), RotaryConfig.parse(d["rot"]))
+        kv = int(d.get("kv_heads") or heads)
+        if kind == "attention":  # no mask block: plain causal; no rot block: nothing rotates
+            rot = RotaryConfig.parse(d["rot"]) if d.get("rot") else RotaryConfig(0, 1.0, None)
+            return MixerConfig(kind, heads, dim, vdim, kv, float(d["scale"]), int((d.get("mask") or {}).get("size", 0)), rot)
         if kind == "delta":
-            return MixerConfig(kind, heads, dim, vdim, int(d["kv_heads"]), conv=int(d["conv"]))
+            return MixerConfig(kind, heads, dim, vdim, kv, conv=int(d["conv"]))
         return MixerConfig(kind, heads, dim, vdim, heads, gate_cap=float(d["gate_cap"]))
 
     def to_dict(self) -> dict:
         d = {"heads": self.heads, "dim": self.dim, "vdim": self.vdim}
         if self.kind == "attention":
-            rot = {"dims": self.rot.dims, "base": self.rot.base}
-            if self.rot.scaling:
-                rot["scaling"] = dict(self.rot.scaling)
-            d.update(kv_heads=self.kv_heads, scale=self.scale, mask={"size": self.chunk}, rot=rot)
+            d.update(kv_heads=self.kv_heads, scale=self.scale)
+            if self.chunk:
+                d["mask"] = {"size": self.chunk}
+            if self.rot.dims:
+                d["rot"] = {"dims": self.rot.dims, "base": self.rot.base}
+                if self.rot.scaling:
+                    d["rot"]["scaling"] = dict(self.rot.scaling)
         elif self.kind == "delta":
             d.update(kv_heads=self.kv_heads, conv=self.conv)
         else:
