@@ -397,11 +397,16 @@ MIXERS = {"attention": attn(3, 1, 16, 24, 21, rot_dims=12), "delta": delta(4, 2,
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
-@pytest.mark.parametrize("name", sorted(MIXERS))
+@pytest.mark.parametrize("name", sorted(MIXERS) + ["mlstm_tiny", "delta_tiny"])
 def test_one_mixer_alone(name, dtype):
-    """a one-layer model without feed-forward: the residual after the layer is embedding + mixer(norm(embedding))"""
-    cfg = one_layer(MIXERS[name])
+    """a one-layer model without feed-forward: the residual after the layer is embedding + mixer(norm(embedding)).  The `_tiny` cases
+    shrink the value projection so that the read-out is of the order of sqrt(eps): only then do the eps of the per-head norm and
+    the matrix memory's divisor max(|n . q|, exp(-m)) -- with m counted from 0 -- change the result (the norm cancels any plain scale)."""
+    cfg = one_layer(MIXERS[name.replace("_tiny", "")])
     w = make_weights(cfg, 11)
+    if name.endswith("_tiny"):
+        w["l0.mix.v"] = (w["l0.mix.v"].float() * 2e-3).to(BF16)
+        w["l0.mix.i.b" if "mlstm" in name else "l0.mix.dt_bias"] -= 3.0  # small input gates: the divisor's floor exp(-m) is what counts
     toks = tokens_for(cfg, 75, 1)
     m = build(cfg, w, dtype)
     m.keep_trail(True)
@@ -555,6 +560,31 @@ def test_long_decoding_and_captured_steps(dtype):
     assert torch.allclose(outs[0], outs[1], atol=1e-5 if dtype == F32 else 2e-2)
     want = oracle_logits(cfg, w, toks)[299:]
     assert close(outs[0], want, dtype)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_batched_decode_steps_of_unequal_requests(dtype):
+    """three prompts of unequal length admitted in one step, then 40 steps that carry one token of each (replayed as a captured
+    launch sequence from the third step on); every request must come out as when it runs alone"""
+    cfg = cfg_general()
+    w = make_weights(cfg, 29, SHARP[dtype])
+    lens = [23, 61, 4]
+    seqs = [tokens_for(cfg, n + 40, 50 + i) for i, n in enumerate(lens)]
+    want = [oracle_logits(cfg, w, q) for q in seqs]
+    m = build(cfg, w, dtype)
+    rids = [m.alloc_request() for _ in lens]
+    got = [[] for _ in lens]
+    out = m.step([(r, q[:n]) for r, q, n in zip(rids, seqs, lens)])
+    for i in range(3):
+        got[i].append(out[i:i + 1])
+    for t in range(40):
+        out = m.step([(r, [q[n + t]]) for r, q, n in zip(rids, seqs, lens)])
+        for i in range(3):
+            got[i].append(out[i:i + 1])
+    assert m.graph_count() > 0
+    for i, n in enumerate(lens):
+        assert close(torch.cat(got[i]), want[i][n - 1:], dtype), i
+    m.close()
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
