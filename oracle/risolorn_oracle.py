@@ -32,10 +32,6 @@ def unit_rms(x, eps):
     return x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + eps)
 
 
-def gelu_tanh(z):
-    return 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))
-
-
 # ---------------------------------------------------------------- rotary embedding
 def rotary_frequencies(rot: dict):
     """(angular frequency per pair [dims / 2], factor on cos and sin)."""
@@ -77,9 +73,12 @@ def attention_mixer(h, w, pre, mx, pos):
     q = (h @ f32(w[pre + "q"]).T + f32(w[pre + "q.b"])).view(T, H, D)
     k = (h @ f32(w[pre + "k"]).T + f32(w[pre + "k.b"])).view(T, G, D)
     v = (h @ f32(w[pre + "v"]).T + f32(w[pre + "v.b"])).view(T, G, Dv)
-    q, k = rotate_interleaved(q, pos, mx["rot"]), rotate_interleaved(k, pos, mx["rot"])
-    size = int(mx["mask"]["size"])
-    see = (pos[None, :] <= pos[:, None]) & ((pos[None, :] // size) == (pos[:, None] // size))
+    if mx.get("rot"):
+        q, k = rotate_interleaved(q, pos, mx["rot"]), rotate_interleaved(k, pos, mx["rot"])
+    see = pos[None, :] <= pos[:, None]
+    if mx.get("mask"):  # chunks are counted from position 0 of the sequence
+        size = int(mx["mask"]["size"])
+        see = see & ((pos[None, :] // size) == (pos[:, None] // size))
     sink = f32(w[pre + "sink"])
     out = torch.zeros(T, H, Dv)
     for hd in range(H):

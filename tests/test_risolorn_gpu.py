@@ -70,6 +70,20 @@ def cfg_wide_heads():
                      vocab=128, width=64)
 
 
+def cfg_recurrent_only():
+    """no layer keeps a paged cache: the pool only counts tokens"""
+    return model_cfg([(mlstm(2, 20, 28, 7.0), moe(4, 2, 2, 1, 24)), (delta(2, 1, 20, 28, 3), moe(4, 2, 2, 2, 24))], vocab=80, width=40)
+
+
+def cfg_attention_only():
+    """no layer keeps a state slot; plain causal attention (no mask block) beside a chunked one, one of them without rotation"""
+    a = attn(2, 1, 16, 16, 0)
+    del a["mixer"]["mask"]
+    b = attn(4, 2, 8, 12, 11)
+    del b["mixer"]["rot"]
+    return model_cfg([(a, moe(4, 2, 2, 1, 24)), (b, None)], vocab=80, width=40)
+
+
 def one_layer(l, mlp=None):
     return model_cfg([(l, mlp)], vocab=64, width=48)
 
@@ -131,7 +145,8 @@ def close(got, want, dtype):
 
 
 SHARP = {F32: 5.0, BF16: 2.0}
-CONFIGS = {"general": cfg_general, "edges": cfg_edges, "wide": cfg_wide_heads}
+CONFIGS = {"general": cfg_general, "edges": cfg_edges, "wide": cfg_wide_heads, "recurrent_only": cfg_recurrent_only,
+           "attention_only": cfg_attention_only}
 
 
 def tokens_for(cfg, n, seed):
