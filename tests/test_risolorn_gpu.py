@@ -496,6 +496,59 @@ def test_prompt_in_portions(dtype, sizes):
     m.close()
 
 
+def random_cfg(seed):
+    """layer order, every size and every constant drawn at random (seeded)"""
+    import random
+    r = random.Random(seed)
+    layers = []
+    for _ in range(r.randint(2, 5)):
+        kind = r.choice(["attention", "delta", "mlstm"])
+        heads = r.choice([1, 2, 3, 4, 6])
+        kv = r.choice([d for d in (1, 2, 3, 4, 6) if heads % d == 0])
+        if kind == "attention":
+            dim = r.choice([8, 12, 20, 32, 40, 64])
+            vdim = dim if r.random() < 0.5 else r.choice([8, 16, 28, 48])
+            l = attn(heads, kv, dim, vdim, r.randint(3, 70), rot_dims=r.choice([0, 2, dim // 2 // 2 * 2, dim]), scaling=r.random() < 0.6,
+                     base=r.choice([100.0, 10000.0, 500000.0]), scale=r.uniform(0.05, 0.4))
+            if l["mixer"]["rot"]["dims"] == 0:
+                del l["mixer"]["rot"]
+        elif kind == "delta":
+            l = delta(heads, kv, r.choice([4, 12, 24, 32, 48, 80]), r.choice([8, 20, 32, 56, 72]), r.randint(1, 5))
+        else:
+            l = mlstm(heads, r.choice([4, 16, 36, 64, 100]), r.choice([8, 24, 40, 64]), r.uniform(2.0, 20.0))
+        mlp = None
+        if r.random() < 0.8:
+            count = r.choice([1, 2, 3, 4])
+            per = r.choice([1, 2, 3, 4])
+            keep = r.randint(1, count)
+            mlp = moe(count * per, r.randint(1, keep * per), count, keep, r.choice([8, 20, 32, 44]))
+        layers.append((l, mlp))
+    return model_cfg(layers, vocab=r.randint(40, 300), width=r.choice([24, 36, 40, 64, 100]), eps=r.choice([1e-5, 1e-6]),
+                     embed=r.uniform(0.5, 4.0), logit=r.uniform(0.2, 2.0))
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("seed", range(12))
+def test_configurations_drawn_at_random(seed, dtype):
+    """a prompt in portions of random sizes (some >= 32 tokens, so that the tensor-core and bucketed kernels run where the sizes
+    allow), then decoded tokens, against the oracle over the whole sequence"""
+    import random
+    cfg = random_cfg(100 + seed)
+    w = make_weights(cfg, 200 + seed, SHARP[dtype])
+    toks = tokens_for(cfg, 120, seed)
+    want = oracle_logits(cfg, w, toks)
+    m = build(cfg, w, dtype)
+    rid = m.alloc_request()
+    r = random.Random(seed)
+    rows, at = [], 0
+    while at < len(toks):
+        n = 1 if at >= 100 else min(r.choice([1, 2, 5, 17, 33, 48]), 100 - at)
+        rows.append(m.step([(rid, toks[at:at + n])], [list(range(n))]))
+        at += n
+    assert close(torch.cat(rows), want, dtype), cfg
+    m.close()
+
+
 @pytest.mark.parametrize("dtype", [F32, BF16])
 def test_unequal_batches_reuse_pages_and_slots(dtype):
     """Seven unequal requests through three request slots and a pool of 18 pages: portions of some beside single tokens of others in
