@@ -259,7 +259,8 @@ def oracle_attention(mx, qkv, bias, sink, lo, hi):
 
 
 # (heads, kv heads, dim, vdim, chunk, rotated entries): bf16 prompts with dim == vdim in {32, 64, 128} run on the tensor cores
-ATTN_SHAPES = [(3, 1, 20, 12, 50, 8), (6, 2, 32, 32, 48, 32), (4, 4, 64, 64, 100, 16), (2, 1, 128, 128, 64, 128), (5, 5, 40, 72, 33, 40)]
+ATTN_SHAPES = [(3, 1, 20, 12, 50, 8), (6, 2, 32, 32, 48, 32), (4, 4, 64, 64, 100, 16), (2, 1, 128, 128, 64, 128), (5, 5, 40, 72, 33, 40),
+               (2, 1, 200, 136, 70, 100), (1, 1, 256, 256, 40, 2)]
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
@@ -408,7 +409,8 @@ def test_gated_experts(lib, dtype, T):
 
 # ------------------------------------------------------------------ one mechanism per model
 MIXERS = {"attention": attn(3, 1, 16, 24, 21, rot_dims=12), "delta": delta(4, 2, 16, 24, 3), "delta_wide": delta(2, 1, 72, 136, 4),
-          "mlstm": mlstm(3, 24, 16, 6.0), "mlstm_wide": mlstm(2, 136, 100, 12.0)}
+          "mlstm": mlstm(3, 24, 16, 6.0), "mlstm_wide": mlstm(2, 136, 100, 12.0), "delta_xwide": delta(2, 2, 160, 24, 2),
+          "mlstm_xwide": mlstm(1, 256, 256, 5.0)}
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
